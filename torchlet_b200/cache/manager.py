@@ -37,6 +37,7 @@ class GroupSpec:
     window: Optional[int]  # None: every key is kept
     entries: tuple  # schedule entries that own a cache layer in this group
     num_pages: int  # pool size, page 0 included
+    planes: int = 2  # rows a token keeps per KV head: key and value, or one latent row
 
 
 class PagePool:

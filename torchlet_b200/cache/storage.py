@@ -1,7 +1,7 @@
 """Device memory of the cache: one tensor of pages per group, one tensor of state rows
 per layer execution that keeps fixed-size state.
 
-Pages of a group: ``[layers in group, num_pages, 2 (k, v), kv_heads, page_size, head_dim]``
+Pages of a group: ``[layers in group, num_pages, planes (2: k, v; 1: a latent row), kv_heads, page_size, head_dim]``
 in the compute dtype, so that a page id means the same page in every layer of the group
 (the reference's single tensor ``[2, L, blocks, kv_heads, block, d]`` has the same
 property, v10_triton_paged_gqa/kvcache.py:19-28) and one (page, kv head) tile of keys is
@@ -22,7 +22,7 @@ from .manager import CacheError, CacheManager, GroupSpec
 class LayerCache:
     """What a mixer sees of the cache for one execution in one step."""
 
-    pages: Optional[torch.Tensor]  # [num_pages, 2, kv_heads, page_size, head_dim]
+    pages: Optional[torch.Tensor]  # [num_pages, planes, kv_heads, page_size, head_dim]
     block_table: Optional[torch.Tensor]  # [requests in step, width] int32
     page_size: int
     state: Optional[torch.Tensor]  # [max_slots, *state shape]
@@ -31,7 +31,7 @@ class LayerCache:
 
 
 def plan_groups(needs: list, num_pages: int) -> tuple[list[GroupSpec], dict]:
-    """Group the executions that own paged history by (kv_heads, head_dim, window).
+    """Group the executions that own paged history by (kv_heads, head_dim, window, planes).
     Returns the groups and a map entry -> (group index, layer index inside the group)."""
     keys, members = [], {}
     for need in needs:
@@ -44,7 +44,7 @@ def plan_groups(needs: list, num_pages: int) -> tuple[list[GroupSpec], dict]:
         members[key].append(need.entry)
     groups, where = [], {}
     for g, key in enumerate(keys):
-        groups.append(GroupSpec(key[0], key[1], key[2], tuple(members[key]), num_pages))
+        groups.append(GroupSpec(key[0], key[1], key[2], tuple(members[key]), num_pages, planes=key[3]))
         for i, entry in enumerate(members[key]):
             where[entry] = (g, i)
     return groups, where
@@ -57,7 +57,7 @@ class CacheStorage:
         self.page_size = page_size
         self.groups, self.where = plan_groups(needs, num_pages)
         element = torch.empty((), dtype=dtype).element_size()
-        need = sum(len(g.entries) * g.num_pages * 2 * g.num_kv_heads * page_size * g.head_dim * element for g in self.groups)
+        need = sum(len(g.entries) * g.num_pages * g.planes * g.num_kv_heads * page_size * g.head_dim * element for g in self.groups)
         if torch.device(device).type == "cuda":
             free, _ = torch.cuda.mem_get_info(device)
             if need > free:
@@ -67,7 +67,7 @@ class CacheStorage:
                     "max_decode_slots")
         self.manager = CacheManager(self.groups, page_size, max_slots, max_seq_len)
         self.pages = [
-            torch.zeros((len(g.entries), g.num_pages, 2, g.num_kv_heads, page_size, g.head_dim), device=device, dtype=dtype)
+            torch.zeros((len(g.entries), g.num_pages, g.planes, g.num_kv_heads, page_size, g.head_dim), device=device, dtype=dtype)
             for g in self.groups
         ]
         self.states = {}

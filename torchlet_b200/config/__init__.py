@@ -1,5 +1,6 @@
 from .engine import EngineConfig, ceil_div
 from .registry import (
+    architecture_name,
     config_class_for,
     config_from_dict,
     known_architectures,
@@ -8,8 +9,10 @@ from .registry import (
 )
 from .spec import LayerSpec, ModelSpec, NormSlot, PartSpec, ScheduleEntry
 from .qwen2 import Qwen2Config
+from .dodonex import DodonexConfig
 
 __all__ = [
+    "DodonexConfig",
     "EngineConfig",
     "LayerSpec",
     "ModelSpec",
@@ -17,6 +20,7 @@ __all__ = [
     "PartSpec",
     "Qwen2Config",
     "ScheduleEntry",
+    "architecture_name",
     "ceil_div",
     "config_class_for",
     "config_from_dict",

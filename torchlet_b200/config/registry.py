@@ -1,4 +1,4 @@
-"""One registry from an architecture's name (``config.json`` ``architectures[0]``)
+"""One registry from an architecture's name (``config.json`` ``architectures[0]``, or ``architecture``)
 to its typed configuration class.
 
 The reference imports ``Qwen2ForCausalLM`` directly (v10_triton_paged_gqa/llm.py:15)
@@ -52,11 +52,19 @@ def config_class_for(name: str) -> type:
         ) from None
 
 
-def config_from_dict(raw: dict):
+def architecture_name(raw: dict) -> str:
+    """The name config.json chooses the model by: ``architectures[0]``, or a plain string under
+    ``architecture``."""
     archs = raw.get("architectures")
-    if not isinstance(archs, (list, tuple)) or not archs:
-        raise ValueError("config.json has no 'architectures' list to choose the model by")
-    return config_class_for(archs[0]).from_dict(raw)
+    if isinstance(archs, (list, tuple)) and archs:
+        return archs[0]
+    if isinstance(raw.get("architecture"), str) and raw["architecture"]:
+        return raw["architecture"]
+    raise ValueError("config.json has no 'architectures' list (or 'architecture' name) to choose the model by")
+
+
+def config_from_dict(raw: dict):
+    return config_class_for(architecture_name(raw)).from_dict(raw)
 
 
 def load_config(model_dir: str | Path):

@@ -43,15 +43,22 @@ class LayerSpec:
     ``prefix + <part prefix>``.  The part prefixes are the checkpoint's own names, set by the
     architecture's configuration; nothing below the configuration layer spells one out.
     ``norms`` holds as many norms as the block arrangement ``block`` asks for, by role.
+    ``feed_forward`` may be None (a layer of a mixer alone).  ``block_params`` are the
+    arrangement's own constants (a residual multiplier, for instance).  ``token_input`` is an
+    optional part that adds something computed from the token ids themselves after the layer's
+    sub-layers (a per-layer token embedding).
     """
 
     prefix: str
     block: str  # arrangement of the parts, e.g. "pre_norm"
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]
     norms: tuple = ()  # of NormSlot
     mixer_prefix: str = "mixer."
     feed_forward_prefix: str = "feed_forward."
+    block_params: dict = field(default_factory=dict)
+    token_input: Optional[PartSpec] = None
+    token_input_prefix: str = "token_input."
 
     def norm(self, role: str) -> NormSlot:
         for slot in self.norms:
@@ -87,6 +94,8 @@ class ModelSpec:
     final_norm_prefix: str
     lm_head_name: str
     tie_word_embeddings: bool
+    embedding_scale: float = 1.0  # the stream starts as embedding[token] * embedding_scale
+    logit_scale: float = 1.0  # logits = (head . normed stream) * logit_scale
 
     def validate(self) -> None:
         if not self.layers:

@@ -12,10 +12,10 @@ namespace {
 using namespace tl;
 
 // ---------------------------------------------------------------- embedding
-// acc[t, :] = float(table[ids[t], :]);  the residual stream starts in float32.
+// acc[t, :] = float(table[ids[t], :]) * scale;  the residual stream starts in float32.
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                             float* __restrict__ acc, int hidden, int vocab) {
+                             float* __restrict__ acc, int hidden, int vocab, float scale) {
   tl::pdl_launch_dependents();  // the next kernel may start its prologue (it waits for us before it reads our output)
   tl::pdl_wait();               // everything before us in the stream is complete and visible
 
@@ -25,24 +25,27 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
   TL_DEBUG_OK(ok, TL_DEBUG_TOKEN, id);  // (an id outside the vocabulary reads as a zero row either way)
   const T* row = table + (size_t)(ok ? id : 0) * hidden;
   float* out = acc + (size_t)t * hidden;
-  for (int j = threadIdx.x; j < hidden; j += blockDim.x) out[j] = ok ? to_float(row[j]) : 0.f;
+  for (int j = threadIdx.x; j < hidden; j += blockDim.x) out[j] = ok ? to_float(row[j]) * scale : 0.f;
 }
 
 // ------------------------------------------------------------------ RMSNorm
 // out[r, :] = acc[row(r), :] * rsqrt(mean(acc[row(r), :]^2) + eps) * w
 // row(r) = rows ? rows[r] : r.  One block per row; the order of the additions
 // depends only on the width, never on which other rows are in the batch.
+// With ``groups`` > 1 a row of ``groups * hidden`` elements is normed in that many equal
+// consecutive parts, each by its own root mean square (one block per part); w covers the row.
 template <typename T, int NT>
 __global__ void __launch_bounds__(NT)
 rms_norm_kernel(const float* __restrict__ acc, const float* __restrict__ w, const int* __restrict__ rows,
-                T* __restrict__ out, int hidden, float eps) {
+                T* __restrict__ out, int hidden, float eps, int groups) {
   tl::pdl_launch_dependents();  // the next kernel may start its prologue (it waits for us before it reads our output)
   tl::pdl_wait();               // everything before us in the stream is complete and visible
 
   __shared__ float scratch[32];
   constexpr int PER = 8;  // elements a thread keeps in registers; longer rows are re-read
-  const int r = blockIdx.x;
-  const float* x = acc + (size_t)(rows ? rows[r] : r) * hidden;
+  const int r = blockIdx.x / groups, part = blockIdx.x % groups;
+  const float* x = acc + ((size_t)(rows ? rows[r] : r) * groups + part) * hidden;
+  w += (size_t)part * hidden;
   float v[PER];
   float ss = 0.f;
 #pragma unroll
@@ -57,7 +60,7 @@ rms_norm_kernel(const float* __restrict__ acc, const float* __restrict__ w, cons
   }
   ss = block_sum<NT>(ss, scratch);
   const float inv = rsqrtf(ss / (float)hidden + eps);
-  T* o = out + (size_t)r * hidden;
+  T* o = out + ((size_t)r * groups + part) * hidden;
 #pragma unroll
   for (int k = 0; k < PER; ++k) {
     const int j = threadIdx.x + k * NT;
@@ -71,15 +74,15 @@ rms_norm_kernel(const float* __restrict__ acc, const float* __restrict__ w, cons
 template <int NT>
 __global__ void __launch_bounds__(NT)
 rms_norm_vec_kernel(const float* __restrict__ acc, const float* __restrict__ w, const int* __restrict__ rows,
-                    __nv_bfloat16* __restrict__ out, int hidden, float eps) {
+                    __nv_bfloat16* __restrict__ out, int hidden, float eps, int groups) {
   tl::pdl_launch_dependents();
   tl::pdl_wait();
 
   __shared__ float scratch[32];
   constexpr int PER = 4;  // float4 a thread
-  const int r = blockIdx.x;
-  const float4* x = reinterpret_cast<const float4*>(acc + (size_t)(rows ? rows[r] : r) * hidden);
-  const float4* w4 = reinterpret_cast<const float4*>(w);
+  const int r = blockIdx.x / groups, part = blockIdx.x % groups;
+  const float4* x = reinterpret_cast<const float4*>(acc + ((size_t)(rows ? rows[r] : r) * groups + part) * hidden);
+  const float4* w4 = reinterpret_cast<const float4*>(w + (size_t)part * hidden);
   const int quads = hidden >> 2;
   float4 v[PER];
   float ss = 0.f;
@@ -94,7 +97,7 @@ rms_norm_vec_kernel(const float* __restrict__ acc, const float* __restrict__ w, 
   }
   ss = block_sum<NT>(ss, scratch);
   const float inv = rsqrtf(ss / (float)hidden + eps);
-  uint2* o = reinterpret_cast<uint2*>(out + (size_t)r * hidden);
+  uint2* o = reinterpret_cast<uint2*>(out + ((size_t)r * groups + part) * hidden);
 #pragma unroll
   for (int k = 0; k < PER; ++k) {
     const int j = threadIdx.x + k * NT;
@@ -237,42 +240,45 @@ TL_DEBUG_READER(tl_elementwise_debug_error)
 extern "C" {
 
 int tl_embed(const void* table, int dtype, const int* ids, float* acc, int tokens, int hidden,
-             int vocab, cudaStream_t stream) {
+             int vocab, float scale, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   const int nt = hidden >= 1024 ? 256 : 128;
   if (dtype == TL_DTYPE_F32)
-    tl::launch_kernel(embed_kernel<float>, tokens, nt, 0, stream, (const float*)table, ids, acc, hidden, vocab);
+    tl::launch_kernel(embed_kernel<float>, tokens, nt, 0, stream, (const float*)table, ids, acc, hidden, vocab, scale);
   else
-    tl::launch_kernel(embed_kernel<__nv_bfloat16>, tokens, nt, 0, stream, (const __nv_bfloat16*)table, ids, acc, hidden, vocab);
+    tl::launch_kernel(embed_kernel<__nv_bfloat16>, tokens, nt, 0, stream, (const __nv_bfloat16*)table, ids, acc, hidden, vocab, scale);
   return TL_LAUNCH_CHECK();
 }
 
 int tl_rms_norm(const float* acc, const float* weight, const int* rows, void* out, int out_dtype,
-                int num_rows, int hidden, float eps, cudaStream_t stream) {
+                int num_rows, int hidden, float eps, int groups, cudaStream_t stream) {
   if (num_rows <= 0) return 0;
+  if (groups <= 0 || hidden % groups) return TL_ERR_UNSUPPORTED;
+  hidden /= groups;  // the width of one normed part
+  num_rows *= groups;
   // the kernel and block size depend on the width, type and alignment alone, so a row's sum
   // never depends on the batch
   const bool aligned = ((reinterpret_cast<uintptr_t>(acc) | reinterpret_cast<uintptr_t>(weight)) & 15) == 0 &&
                        (reinterpret_cast<uintptr_t>(out) & 7) == 0;
   if (out_dtype == TL_DTYPE_BF16 && hidden % 4 == 0 && hidden <= 8192 && aligned) {
     if (hidden <= 2048)
-      tl::launch_kernel(rms_norm_vec_kernel<128>, num_rows, 128, 0, stream, acc, weight, rows, (__nv_bfloat16*)out, hidden, eps);
+      tl::launch_kernel(rms_norm_vec_kernel<128>, num_rows, 128, 0, stream, acc, weight, rows, (__nv_bfloat16*)out, hidden, eps, groups);
     else if (hidden <= 4096)
-      tl::launch_kernel(rms_norm_vec_kernel<256>, num_rows, 256, 0, stream, acc, weight, rows, (__nv_bfloat16*)out, hidden, eps);
+      tl::launch_kernel(rms_norm_vec_kernel<256>, num_rows, 256, 0, stream, acc, weight, rows, (__nv_bfloat16*)out, hidden, eps, groups);
     else
-      tl::launch_kernel(rms_norm_vec_kernel<512>, num_rows, 512, 0, stream, acc, weight, rows, (__nv_bfloat16*)out, hidden, eps);
+      tl::launch_kernel(rms_norm_vec_kernel<512>, num_rows, 512, 0, stream, acc, weight, rows, (__nv_bfloat16*)out, hidden, eps, groups);
     return TL_LAUNCH_CHECK();
   }
   if (hidden <= 2048) {
     if (out_dtype == TL_DTYPE_F32)
-      tl::launch_kernel(rms_norm_kernel<float, 256>, num_rows, 256, 0, stream, acc, weight, rows, (float*)out, hidden, eps);
+      tl::launch_kernel(rms_norm_kernel<float, 256>, num_rows, 256, 0, stream, acc, weight, rows, (float*)out, hidden, eps, groups);
     else
-      tl::launch_kernel(rms_norm_kernel<__nv_bfloat16, 256>, num_rows, 256, 0, stream, acc, weight, rows, (__nv_bfloat16*)out, hidden, eps);
+      tl::launch_kernel(rms_norm_kernel<__nv_bfloat16, 256>, num_rows, 256, 0, stream, acc, weight, rows, (__nv_bfloat16*)out, hidden, eps, groups);
   } else {
     if (out_dtype == TL_DTYPE_F32)
-      tl::launch_kernel(rms_norm_kernel<float, 512>, num_rows, 512, 0, stream, acc, weight, rows, (float*)out, hidden, eps);
+      tl::launch_kernel(rms_norm_kernel<float, 512>, num_rows, 512, 0, stream, acc, weight, rows, (float*)out, hidden, eps, groups);
     else
-      tl::launch_kernel(rms_norm_kernel<__nv_bfloat16, 512>, num_rows, 512, 0, stream, acc, weight, rows, (__nv_bfloat16*)out, hidden, eps);
+      tl::launch_kernel(rms_norm_kernel<__nv_bfloat16, 512>, num_rows, 512, 0, stream, acc, weight, rows, (__nv_bfloat16*)out, hidden, eps, groups);
   }
   return TL_LAUNCH_CHECK();
 }

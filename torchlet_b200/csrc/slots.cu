@@ -50,7 +50,7 @@ slot_gather_kernel(const int* __restrict__ command, int b, int groups, int max_s
       lane_token[lane] = 0;
       lane_position[lane] = 0;
       lane_kv_before[lane] = 0;
-      lane_slot[lane] = 0;
+      lane_slot[lane] = -1;  // a mixer with per-slot state leaves a padding lane's state alone
       lane_seed[lane] = 0;
       lane_temperature[lane] = 0.f;
       lane_counter[lane] = 0;

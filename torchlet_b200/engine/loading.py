@@ -13,13 +13,16 @@ import torch
 from ..config import load_config
 from ..logger import logger
 from ..parts import LayeredModel, expected_tensors
-from ..weights import check_and_normalise, load_checkpoint
+from ..weights import check_and_normalise, checkpoint_shapes, load_checkpoint
 
 TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32, "bf16": torch.bfloat16, "fp32": torch.float32}
 
 
 def build_model(config, tensors: dict, dtype, device="cuda:0") -> LayeredModel:
     """A ``LayeredModel`` from a typed configuration and tensors by name (any device)."""
+    if hasattr(config, "with_tensor_shapes"):  # sizes that only the tensors give
+        lazy = hasattr(tensors, "meta")
+        config = config.with_tensor_shapes({n: (tensors.meta(n)[0] if lazy else tuple(tensors[n].shape)) for n in tensors})
     spec = config.model_spec()
     tensors = check_and_normalise(tensors, expected_tensors(spec))
     torch_dtype = TORCH_DTYPES[dtype] if isinstance(dtype, str) else dtype
@@ -38,6 +41,8 @@ def build_model(config, tensors: dict, dtype, device="cuda:0") -> LayeredModel:
 
 def load_model(model_dir: str | Path, dtype="bfloat16", device="cuda:0") -> LayeredModel:
     config = load_config(model_dir)
+    if hasattr(config, "with_tensor_shapes"):
+        config = config.with_tensor_shapes(checkpoint_shapes(model_dir))
     spec = config.model_spec()
     tensors = load_checkpoint(model_dir, expected_tensors(spec))
     return build_model(config, tensors, dtype, device)

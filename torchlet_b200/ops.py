@@ -33,8 +33,8 @@ def dtype_code(dtype: torch.dtype) -> int:
 
 _SIGNATURES = {
     "elementwise": {
-        "tl_embed": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
-        "tl_rms_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
+        "tl_embed": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
+        "tl_rms_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p],
         "tl_rope_kv": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                        c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "tl_elementwise_debug_error": [c_void_p],
@@ -86,6 +86,35 @@ _SIGNATURES = {
         "tl_slot_command_words": [c_int, c_int],
         "tl_slot_record_rows": [],
         "tl_slots_debug_error": [c_void_p],
+    },
+    "stream_ops": {
+        "tl_fill_zero": [c_void_p, c_longlong, c_void_p],
+        "tl_scale": [c_void_p, c_float, c_longlong, c_void_p],
+        "tl_scaled_add": [c_void_p, c_void_p, c_float, c_void_p, c_longlong, c_void_p],
+        "tl_rms_scaled_add": [c_void_p, c_void_p, c_void_p, c_float, c_float, c_int, c_int, c_void_p],
+        "tl_gated_token_embed": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
+        "tl_clamped_glu": [c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p],
+        "tl_stream_ops_debug_error": [c_void_p],
+    },
+    "delta_rule": {
+        "tl_delta_prepare": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                             c_void_p],
+        "tl_delta_scan": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                          c_int, c_void_p],
+        "tl_delta_finish": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
+                            c_void_p],
+        "tl_delta_rule_debug_error": [c_void_p],
+    },
+    "latent_attention": {
+        "tl_latent_prepare": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_float,
+                              c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_int,
+                              c_int, c_void_p],
+        "tl_latent_absorb_q": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                               c_int, c_int, c_int, c_void_p],
+        "tl_latent_attention": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+        "tl_latent_expand_o": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "tl_latent_attention_debug_error": [c_void_p],
     },
     "sampling": {
         "tl_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -143,20 +172,22 @@ def _need_cuda(*tensors) -> None:
 
 
 # ------------------------------------------------------------------ wrappers
-def embed(table: torch.Tensor, ids: torch.Tensor, acc: torch.Tensor) -> None:
-    """acc[t] = float32(table[ids[t]]);  ids int32 [T], acc float32 [T, hidden]."""
+def embed(table: torch.Tensor, ids: torch.Tensor, acc: torch.Tensor, scale: float = 1.0) -> None:
+    """acc[t] = float32(table[ids[t]]) * scale;  ids int32 [T], acc float32 [T, hidden]."""
     _need_cuda(table, ids, acc)
     tokens, hidden = acc.shape
     assert ids.dtype == torch.int32 and acc.dtype == torch.float32 and acc.is_contiguous()
     assert table.is_contiguous() and table.shape[1] == hidden
     code = _fn("elementwise", "tl_embed")(
         table.data_ptr(), dtype_code(table.dtype), ids.data_ptr(), acc.data_ptr(), tokens, hidden,
-        table.shape[0], _stream())
+        table.shape[0], float(scale), _stream())
     _check(code, "embed")
 
 
-def rms_norm(acc: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, rows=None) -> None:
-    """out[r] = rmsnorm(acc[rows[r] or r]) * weight;  acc float32, weight float32."""
+def rms_norm(acc: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, rows=None,
+             groups: int = 1) -> None:
+    """out[r] = rmsnorm(acc[rows[r] or r]) * weight;  acc float32, weight float32.  ``groups`` > 1:
+    every row is normed in that many equal consecutive parts, each by its own root mean square."""
     _need_cuda(acc, weight, out, rows)
     hidden = acc.shape[1]
     num_rows = out.shape[0]
@@ -165,7 +196,7 @@ def rms_norm(acc: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Ten
     assert rows is None or (rows.dtype == torch.int32 and rows.numel() >= num_rows)
     code = _fn("elementwise", "tl_rms_norm")(
         acc.data_ptr(), weight.data_ptr(), _ptr(rows), out.data_ptr(), dtype_code(out.dtype), num_rows,
-        hidden, float(eps), _stream())
+        hidden, float(eps), int(groups), _stream())
     _check(code, "rms_norm")
 
 
@@ -245,6 +276,164 @@ def sample(logits, out, temperature=None, seed=None, counter=None) -> None:
         logits.data_ptr(), logits.stride(0), rows, vocab, _ptr(temperature), _ptr(seed), _ptr(counter),
         out.data_ptr(), _ptr(scratch), scratch.numel() * 4 if scratch is not None else 0, _stream())
     _check(code, "sample", 2 if chunks > 1 else 1)
+
+
+# ------------------------------------------------- around the residual stream
+def fill_zero(x: torch.Tensor) -> None:
+    """x = 0;  float32, contiguous, a multiple of 4 elements."""
+    _need_cuda(x)
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    _check(_fn("stream_ops", "tl_fill_zero")(x.data_ptr(), x.numel(), _stream()), "fill_zero")
+
+
+def scale_(x: torch.Tensor, alpha: float) -> None:
+    """x *= alpha;  float32, contiguous."""
+    _need_cuda(x)
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    _check(_fn("stream_ops", "tl_scale")(x.data_ptr(), float(alpha), x.numel(), _stream()), "scale")
+
+
+def scaled_add(acc: torch.Tensor, delta: torch.Tensor, m: float, cast: torch.Tensor | None = None) -> None:
+    """acc += m * delta (float32); ``cast`` (bfloat16, same shape) also receives the updated acc."""
+    _need_cuda(acc, delta, cast)
+    assert acc.dtype == delta.dtype == torch.float32 and acc.shape == delta.shape
+    assert acc.is_contiguous() and delta.is_contiguous()
+    assert cast is None or (cast.dtype == torch.bfloat16 and cast.shape == acc.shape and cast.is_contiguous())
+    code = _fn("stream_ops", "tl_scaled_add")(acc.data_ptr(), delta.data_ptr(), float(m), _ptr(cast), acc.numel(),
+                                              _stream())
+    _check(code, "scaled_add")
+
+
+def rms_scaled_add(acc: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, m: float, eps: float) -> None:
+    """acc[r] += m * y[r] / sqrt(mean(y[r]^2) + eps) * weight;  all float32."""
+    _need_cuda(acc, y, weight)
+    rows, hidden = acc.shape
+    assert acc.dtype == y.dtype == weight.dtype == torch.float32 and y.shape == acc.shape
+    assert acc.is_contiguous() and y.is_contiguous() and weight.numel() == hidden
+    code = _fn("stream_ops", "tl_rms_scaled_add")(acc.data_ptr(), y.data_ptr(), weight.data_ptr(), float(m),
+                                                  float(eps), rows, hidden, _stream())
+    _check(code, "rms_scaled_add")
+
+
+def gated_token_embed(gate: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t] = gelu_tanh(gate[t]) * table[ids[t]];  gate float32 [T, dim], table and out in the compute type."""
+    _need_cuda(gate, table, ids, out)
+    tokens, dim = out.shape
+    assert gate.dtype == torch.float32 and gate.shape == out.shape and gate.is_contiguous() and out.is_contiguous()
+    assert table.dtype == out.dtype and table.shape[1] == dim and table.stride(1) == 1 and ids.dtype == torch.int32
+    code = _fn("stream_ops", "tl_gated_token_embed")(
+        gate.data_ptr(), table.data_ptr(), table.stride(0), dtype_code(out.dtype), ids.data_ptr(), table.shape[0],
+        out.data_ptr(), tokens, dim, _stream())
+    _check(code, "gated_token_embed")
+
+
+def clamped_glu(gate_up: torch.Tensor, out: torch.Tensor, limit: float, alpha: float) -> None:
+    """out = g * sigmoid(alpha * g) * (u + 1) with g = min(gate_up[:, :I], limit) and
+    u = clamp(gate_up[:, I:], -limit, limit)."""
+    _need_cuda(gate_up, out)
+    tokens, inter = out.shape
+    assert gate_up.shape == (tokens, 2 * inter) and gate_up.is_contiguous() and out.is_contiguous()
+    assert gate_up.dtype == out.dtype
+    code = _fn("stream_ops", "tl_clamped_glu")(gate_up.data_ptr(), out.data_ptr(), dtype_code(out.dtype), tokens,
+                                               inter, float(limit), float(alpha), _stream())
+    _check(code, "clamped_glu")
+
+
+# ------------------------------------------------------------ delta-rule mixer
+def delta_prepare(proj, w2, w0, a_bias, gates, heads: int, dim: int, rank: int) -> None:
+    """From the float32 projections ``proj`` [T, 5 H D + rank] (r | k | v | g | a' | l) to
+    ``gates`` [T, H, 3, D]: decay w, unit key u and a * u of every key channel (csrc/delta_rule.cu)."""
+    _need_cuda(proj, w2, w0, a_bias, gates)
+    tokens = proj.shape[0]
+    assert proj.dtype == torch.float32 and proj.stride(1) == 1 and proj.shape[1] == 5 * heads * dim + rank
+    assert w2.dtype == w0.dtype == a_bias.dtype == gates.dtype == torch.float32
+    assert w2.is_contiguous() and w2.shape == (heads * dim, rank) and gates.is_contiguous()
+    assert gates.numel() == tokens * heads * 3 * dim
+    code = _fn("delta_rule", "tl_delta_prepare")(proj.data_ptr(), proj.stride(0), w2.data_ptr(), w0.data_ptr(),
+                                                 a_bias.data_ptr(), gates.data_ptr(), tokens, heads, dim, rank,
+                                                 _stream())
+    _check(code, "delta_prepare")
+
+
+def delta_scan(proj, gates, req_indptr, slots, state, out, requests: int, heads: int, dim: int) -> None:
+    """Walks each request's tokens of the step through its slot's state [H, D, D] (float32);
+    ``out`` float32 [T, H D] receives S_t^T r_t.  A request whose slot is negative is padding."""
+    _need_cuda(proj, gates, req_indptr, slots, state, out)
+    assert state.dtype == out.dtype == torch.float32 and state.is_contiguous() and out.is_contiguous()
+    assert state.shape[1:] == (heads, dim, dim) and req_indptr.dtype == slots.dtype == torch.int32
+    code = _fn("delta_rule", "tl_delta_scan")(proj.data_ptr(), proj.stride(0), gates.data_ptr(), req_indptr.data_ptr(),
+                                              slots.data_ptr(), state.data_ptr(), out.data_ptr(), requests, heads, dim,
+                                              state.shape[0], _stream())
+    _check(code, "delta_scan")
+
+
+def delta_finish(o, proj, weight, out, heads: int, dim: int, eps: float) -> None:
+    """out = o / rms(o per head) * weight * sigmoid(g), g read from ``proj``; out in the compute type."""
+    _need_cuda(o, proj, weight, out)
+    tokens = o.shape[0]
+    assert o.dtype == weight.dtype == torch.float32 and o.is_contiguous() and out.is_contiguous()
+    assert out.shape == o.shape == (tokens, heads * dim)
+    code = _fn("delta_rule", "tl_delta_finish")(o.data_ptr(), proj.data_ptr(), proj.stride(0), weight.data_ptr(),
+                                                out.data_ptr(), dtype_code(out.dtype), tokens, heads, dim, float(eps),
+                                                _stream())
+    _check(code, "delta_finish")
+
+
+# ------------------------------------------------------------ latent attention
+def latent_prepare(down, q_rank, kv_rank, rot_dim, rot_dims, q_norm, kv_norm, inv_freq, eps, positions, token_req,
+                   block_table, pages, page_size, q_latent, write_kv: bool) -> None:
+    """Norms of the query latent and (``write_kv``) of the key/value latent, rotation of the shared
+    key part, and the write of the token's cache row (csrc/latent_attention.cu)."""
+    _need_cuda(down, q_norm, kv_norm, inv_freq, positions, token_req, block_table, pages, q_latent)
+    tokens = down.shape[0]
+    assert down.dtype == torch.float32 and down.stride(1) == 1
+    assert down.shape[1] == q_rank + ((kv_rank + rot_dim) if write_kv else 0)
+    assert q_latent.is_contiguous() and q_latent.shape == (tokens, q_rank)
+    assert not write_kv or (pages.dtype == q_latent.dtype and pages.is_contiguous())
+    code = _fn("latent_attention", "tl_latent_prepare")(
+        down.data_ptr(), down.stride(0), q_rank, kv_rank, rot_dim, rot_dims, q_norm.data_ptr(), _ptr(kv_norm),
+        inv_freq.data_ptr(), float(eps), positions.data_ptr(), token_req.data_ptr(), block_table.data_ptr(),
+        block_table.shape[1], pages.data_ptr(), dtype_code(q_latent.dtype), page_size, pages.shape[0],
+        q_latent.data_ptr(), 1 if write_kv else 0, tokens, _stream())
+    _check(code, "latent_prepare")
+
+
+def latent_absorb_q(q, uk, inv_freq, positions, q_abs, heads, dim, rot_dim, rot_dims, kv_rank) -> None:
+    """q float32 [T, H (dim + rot)] -> q_abs [T, H, kv_rank + rot]: W_uk,h^T q_plain and the rotated part."""
+    _need_cuda(q, uk, inv_freq, positions, q_abs)
+    tokens = q.shape[0]
+    assert q.dtype == torch.float32 and q.stride(1) == 1 and q.shape[1] == heads * (dim + rot_dim)
+    assert uk.dtype == q_abs.dtype and uk.is_contiguous() and uk.shape == (heads * dim, kv_rank)
+    assert q_abs.is_contiguous() and q_abs.numel() == tokens * heads * (kv_rank + rot_dim)
+    code = _fn("latent_attention", "tl_latent_absorb_q")(
+        q.data_ptr(), q.stride(0), uk.data_ptr(), dtype_code(uk.dtype), inv_freq.data_ptr(), positions.data_ptr(),
+        q_abs.data_ptr(), tokens, heads, dim, rot_dim, rot_dims, kv_rank, _stream())
+    _check(code, "latent_absorb_q")
+
+
+def latent_attention(q_abs, pages, block_table, token_req, positions, out, tokens, heads, dk, dv, page_size,
+                     scale) -> None:
+    """Causal attention of every (token, head) over the cached rows of its request, in the latent
+    space: keys are whole rows (dk), values their first dv entries; one warp per (token, head)."""
+    _need_cuda(q_abs, pages, block_table, token_req, positions, out)
+    assert q_abs.dtype == pages.dtype == out.dtype and q_abs.is_contiguous() and out.is_contiguous()
+    assert pages.is_contiguous()
+    code = _fn("latent_attention", "tl_latent_attention")(
+        q_abs.data_ptr(), pages.data_ptr(), dtype_code(out.dtype), block_table.data_ptr(), block_table.shape[1],
+        token_req.data_ptr(), positions.data_ptr(), out.data_ptr(), tokens, heads, dk, dv, page_size, float(scale),
+        pages.shape[0], _stream())
+    _check(code, "latent_attention")
+
+
+def latent_expand_o(o_lat, uv, out, heads, vdim, kv_rank) -> None:
+    """out[t, h] = W_uv,h o_lat[t, h];  uv [H vdim, kv_rank], out [T, H vdim]."""
+    _need_cuda(o_lat, uv, out)
+    tokens = out.shape[0]
+    assert o_lat.dtype == uv.dtype == out.dtype and o_lat.is_contiguous() and uv.is_contiguous() and out.is_contiguous()
+    assert uv.shape == (heads * vdim, kv_rank) and out.shape == (tokens, heads * vdim)
+    code = _fn("latent_attention", "tl_latent_expand_o")(o_lat.data_ptr(), uv.data_ptr(), out.data_ptr(),
+                                                         dtype_code(out.dtype), tokens, heads, vdim, kv_rank, _stream())
+    _check(code, "latent_expand_o")
 
 
 # ---------------------------------------------------------------- slot records
@@ -521,7 +710,8 @@ def debug_errors() -> list:
     offending value) for every loaded library whose check failed; reading clears.  Always empty
     in the ordinary build (``TORCHLET_B200_DEBUG`` unset), whose kernels carry no checks."""
     found = []
-    for library in ("elementwise", "attention_generic", "attention_mma", "decode_fused", "slots"):
+    for library in ("elementwise", "attention_generic", "attention_mma", "decode_fused", "slots", "stream_ops",
+                    "delta_rule", "latent_attention"):
         if any(name in _functions for name in _SIGNATURES[library]):
             value = ctypes.c_int(0)
             code = _fn(library, f"tl_{library}_debug_error")(ctypes.byref(value))

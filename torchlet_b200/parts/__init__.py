@@ -14,15 +14,17 @@ from .base import (
     Part,
     Positions,
     StateSpec,
+    TOKEN_INPUTS,
     TensorSpec,
+    TokenInput,
     build_part,
 )
-from . import attention, block, norm, rotary, swiglu  # noqa: F401  (registration)
+from . import attention, block, clamped_glu, delta_rule, latent_attention, norm, rotary, swiglu, token_input  # noqa: F401  (registration)
 from .linear import Linear
 from .model import LayeredModel, expected_tensors
 
 __all__ = [
     "BLOCKS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITIONS", "Block", "FeedForward", "KVSpec",
-    "LayeredModel", "Linear", "Mixer", "Norm", "Part", "Positions", "StateSpec", "TensorSpec",
+    "LayeredModel", "Linear", "Mixer", "Norm", "Part", "Positions", "StateSpec", "TOKEN_INPUTS", "TensorSpec", "TokenInput",
     "build_part", "expected_tensors",
 ]

@@ -35,14 +35,17 @@ class TensorSpec:
 @dataclass(frozen=True)
 class KVSpec:
     """Per-token history a mixer keeps in pages: keys and values of every token,
-    or of the last ``window`` tokens only."""
+    or of the last ``window`` tokens only.  ``planes`` is how many rows of ``head_dim`` a token
+    keeps per KV head: 2 (a key and a value), or 1 for a mixer whose keys and values are
+    expanded from one cached row (a latent)."""
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    planes: int = 2
 
     def group_key(self) -> tuple:
-        return (self.num_kv_heads, self.head_dim, self.window)
+        return (self.num_kv_heads, self.head_dim, self.window, self.planes)
 
 
 @dataclass(frozen=True)
@@ -128,21 +131,34 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class TokenInput(Part):
+    """Something added to the stream after a layer's sub-layers that is computed from the
+    step's token ids themselves (``ctx.tokens``) and the stream."""
+
+    def forward(self, ctx, acc, m: float = 1.0) -> None:
+        """acc += m * f(acc, tokens)."""
+        raise NotImplementedError
+
+
 class Block:
     """An arrangement of a layer's parts around the residual stream.  ``norm_roles`` names the
     norms the arrangement needs; the layer's description must hold one for each role, and
-    ``norms`` maps the roles to the built parts."""
+    ``norms`` maps the roles to the built parts.  ``feed_forward`` and ``token_input`` may be
+    None; ``params`` are the arrangement's own constants from the layer's description."""
 
     kind: str = ""
     norm_roles: tuple = ()
 
-    def __init__(self, mixer: Mixer, feed_forward: FeedForward, norms: dict):
+    def __init__(self, mixer: Mixer, feed_forward: Optional[FeedForward], norms: dict, params: Optional[dict] = None,
+                 token_input: Optional[TokenInput] = None):
         missing = [role for role in self.norm_roles if role not in norms]
         if missing:
             raise ValueError(f"block arrangement {self.kind!r} needs norms for the roles {missing}")
         self.mixer = mixer
         self.feed_forward = feed_forward
         self.norms = dict(norms)
+        self.params = dict(params or {})
+        self.token_input = token_input
 
     def forward(self, ctx, acc, cache) -> None:
         raise NotImplementedError
@@ -178,6 +194,7 @@ FEED_FORWARDS = _Registry("feed-forward")
 NORMS = _Registry("norm")
 POSITIONS = _Registry("position encoding")
 BLOCKS = _Registry("block arrangement")
+TOKEN_INPUTS = _Registry("token input")
 
 
 def build_part(registry: _Registry, spec: PartSpec) -> Part:

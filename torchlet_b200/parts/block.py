@@ -3,9 +3,12 @@
 "pre_norm": h = x + mixer(norm(x)); x' = h + feed_forward(norm(h))
 (v10_triton_paged_gqa/layer/transformer_block.py:37-40).  The stream ``acc`` is
 float32; mixer and feed-forward add into it.
+
+"parallel_scaled": one norm, mixer and feed-forward side by side, a residual multiplier.
 """
 from __future__ import annotations
 
+from .. import ops
 from .base import BLOCKS, Block
 
 
@@ -18,3 +21,28 @@ class PreNormBlock(Block):
         self.mixer.forward(ctx, x, acc, cache)
         x = self.norms["feed_forward_norm"].apply(ctx, acc)
         self.feed_forward.forward(ctx, x, acc)
+
+
+@BLOCKS.register("parallel_scaled")
+class ParallelScaledBlock(Block):
+    """h = norm(x); x' = x + m (mixer(h) + feed_forward(h)); then the layer's token input, if it
+    has one, adds m * f(x', tokens).  One norm, both sub-layers read its output; ``m`` is the
+    arrangement's parameter ``residual_mult`` (default 1).  The sub-layers add into a zeroed
+    float32 stream of their own, so the scaled residual sum is one float32 operation."""
+
+    norm_roles = ("shared_norm",)
+
+    def forward(self, ctx, acc, cache) -> None:
+        m = float(self.params.get("residual_mult", 1.0))
+        x = self.norms["shared_norm"].apply(ctx, acc)
+        delta = ctx.buffer("parallel.delta", tuple(acc.shape), acc.dtype)
+        ops.fill_zero(delta)
+        self.mixer.forward(ctx, x, delta, cache)
+        if self.feed_forward is not None:
+            self.feed_forward.forward(ctx, x, delta)
+        ctx.flush_pending()
+        token_input = self.token_input
+        cast = token_input.wants_cast(ctx, acc) if token_input is not None else None
+        ops.scaled_add(acc, delta, m, cast)
+        if token_input is not None:
+            token_input.forward(ctx, acc, m, cast=cast)

@@ -1,0 +1,110 @@
+"""Latent attention: queries, keys and values come through low-rank latents, and a token's
+cache row is [c (kv_rank) | k_rot (rot_dim)], shared by all heads.
+
+    c_q = rmsnorm(W_dq x) * w_q            q[h] = W_uq,h c_q = [q_plain (dim) | q_rot (rot_dim)]
+    [c', k'] = W_dkv x                     c = rmsnorm(c') * w_kv,   k_rot = rotate(k')
+    key[h] = [W_uk,h c | k_rot]            value[h] = W_uv,h c
+    score = scale (q_plain . W_uk,h c + rotate(q_rot) . k_rot),  causal softmax,  out = W_o [heads]
+
+The attention itself runs in the latent space (csrc/latent_attention.cu): W_uk,h is folded into
+the query and W_uv,h applied after the weighted sum of cached rows, so no key or value of a
+cached token is ever expanded and prompt portions, single tokens and mixed batches are one code
+path.  A layer with ``kv_from`` has no W_dkv and reads another layer's cache rows.
+
+Parameters: ``hidden_size``, ``num_heads``, ``head_dim`` (unrotated), ``rot_dim``, ``v_dim``,
+``q_rank``, ``kv_rank``, ``scale``, ``rot_base``, ``rot_dims`` (how many of the rot_dim entries
+are rotated), ``eps``, ``own_kv``.  Tensors below the prefix: dq, dq.norm, uq, [dkv, dkv.norm],
+uk, uv, o.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..config.spec import PartSpec
+from .base import MIXERS, KVSpec, Mixer, TensorSpec
+from .linear import Linear
+
+
+@MIXERS.register("latent_attention")
+class LatentAttentionMixer(Mixer):
+    graph_safe = True  # nothing is planned on the host for single-token steps
+
+    def __init__(self, spec: PartSpec):
+        super().__init__(spec)
+        p = spec.params
+        self.hidden_size = int(p["hidden_size"])
+        self.num_heads = int(p["num_heads"])
+        self.head_dim = int(p["head_dim"])
+        self.rot_dim = int(p["rot_dim"])
+        self.v_dim = int(p["v_dim"])
+        self.q_rank, self.kv_rank = int(p["q_rank"]), int(p["kv_rank"])
+        self.scale = float(p["scale"])
+        self.rot_base = float(p["rot_base"])
+        self.rot_dims = int(p.get("rot_dims", self.rot_dim))
+        self.eps = float(p["eps"])
+        self.own_kv = bool(p.get("own_kv", True))
+        if self.rot_dims % 2 or self.rot_dims > self.rot_dim:
+            raise ValueError("rot_dims must be even and at most rot_dim")
+        if self.kv_rank > 512:
+            raise ValueError(f"kv_rank {self.kv_rank} is not supported by the latent attention kernels (up to 512)")
+        self.row = self.kv_rank + self.rot_dim  # a token's cache row
+        self.down_proj: Linear | None = None
+        self.uq_proj: Linear | None = None
+        self.o_proj: Linear | None = None
+        self.uk = self.uv = self.q_norm = self.kv_norm = self.inv_freq = None
+
+    def kv_spec(self) -> KVSpec:
+        return KVSpec(1, self.row, None, planes=1)
+
+    @classmethod
+    def expected_tensors(cls, spec: PartSpec, prefix: str) -> list[TensorSpec]:
+        p = spec.params
+        hidden, H = int(p["hidden_size"]), int(p["num_heads"])
+        D, R, V = int(p["head_dim"]), int(p["rot_dim"]), int(p["v_dim"])
+        q_rank, kv_rank = int(p["q_rank"]), int(p["kv_rank"])
+        out = [TensorSpec(prefix + "dq", (q_rank, hidden)), TensorSpec(prefix + "dq.norm", (q_rank,), init="ones"),
+               TensorSpec(prefix + "uq", (H * (D + R), q_rank))]
+        if p.get("own_kv", True):
+            out += [TensorSpec(prefix + "dkv", (kv_rank + R, hidden)),
+                    TensorSpec(prefix + "dkv.norm", (kv_rank,), init="ones")]
+        out += [TensorSpec(prefix + "uk", (H * D, kv_rank)), TensorSpec(prefix + "uv", (H * V, kv_rank)),
+                TensorSpec(prefix + "o", (hidden, H * V))]
+        return out
+
+    def load(self, tensors: dict, prefix: str, device, dtype) -> None:
+        down = [tensors[prefix + "dq"]] + ([tensors[prefix + "dkv"]] if self.own_kv else [])
+        self.down_proj = Linear(torch.cat(down, dim=0), None, device, dtype)
+        self.uq_proj = Linear(tensors[prefix + "uq"], None, device, dtype)
+        self.o_proj = Linear(tensors[prefix + "o"], None, device, dtype)
+        self.uk = tensors[prefix + "uk"].to(device=device, dtype=dtype).contiguous()
+        self.uv = tensors[prefix + "uv"].to(device=device, dtype=dtype).contiguous()
+        f32 = lambda name: tensors[prefix + name].to(device=device, dtype=torch.float32).contiguous()
+        self.q_norm = f32("dq.norm")
+        self.kv_norm = f32("dkv.norm") if self.own_kv else None
+        # base^(-2i/dims), taken in float64 and rounded once
+        i = torch.arange(self.rot_dims // 2, dtype=torch.float64)
+        self.inv_freq = (self.rot_base ** (-2.0 * i / max(self.rot_dims, 1))).to(torch.float32).to(device)
+
+    def forward(self, ctx, x, acc, cache) -> None:
+        tokens, H = x.shape[0], self.num_heads
+        if self.own_kv != cache.writable:
+            raise ValueError("a latent attention layer writes the cache exactly when it has a W_dkv of its own")
+        down = ctx.buffer("latent.down", (tokens, self.down_proj.out_features), torch.float32)
+        self.down_proj.forward(x, down)
+        c_q = ctx.buffer("latent.c_q", (tokens, self.q_rank), ctx.dtype)
+        ops.latent_prepare(down, self.q_rank, self.kv_rank, self.rot_dim, self.rot_dims, self.q_norm, self.kv_norm,
+                           self.inv_freq, self.eps, ctx.positions, ctx.token_req, cache.block_table, cache.pages,
+                           cache.page_size, c_q, write_kv=self.own_kv)
+        q = ctx.buffer("latent.q", (tokens, H * (self.head_dim + self.rot_dim)), torch.float32)
+        self.uq_proj.forward(c_q, q)
+        q_abs = ctx.buffer("latent.q_abs", (tokens, H * self.row), ctx.dtype)
+        ops.latent_absorb_q(q, self.uk, self.inv_freq, ctx.positions, q_abs, H, self.head_dim, self.rot_dim,
+                            self.rot_dims, self.kv_rank)
+        o_lat = ctx.buffer("latent.o_lat", (tokens, H * self.kv_rank), ctx.dtype)
+        ops.latent_attention(q_abs, cache.pages, cache.block_table, ctx.token_req, ctx.positions, o_lat, tokens, H,
+                             self.row, self.kv_rank, cache.page_size, self.scale)
+        out = ctx.buffer("latent.out", (tokens, H * self.v_dim), ctx.dtype)
+        ops.latent_expand_o(o_lat, self.uv, out, H, self.v_dim, self.kv_rank)
+        if not self.o_proj.accumulate_later(ctx, out, acc):
+            self.o_proj.forward(out, acc, accumulate=True)

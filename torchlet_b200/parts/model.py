@@ -11,7 +11,7 @@ import torch
 
 from .. import ops
 from ..config.spec import ModelSpec
-from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, KVSpec, StateSpec, TensorSpec, build_part
+from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, TOKEN_INPUTS, KVSpec, StateSpec, TensorSpec, build_part
 from .linear import Linear
 
 
@@ -30,7 +30,10 @@ def _layer_parts(layer) -> list:
     order their tensors are listed and loaded.  The names come from the layer's description."""
     parts = [(NORMS, slot.part, layer.prefix + slot.prefix, slot.role) for slot in layer.norms]
     parts.insert(min(1, len(parts)), (MIXERS, layer.mixer, layer.prefix + layer.mixer_prefix, "mixer"))
-    parts.append((FEED_FORWARDS, layer.feed_forward, layer.prefix + layer.feed_forward_prefix, "feed_forward"))
+    if layer.feed_forward is not None:
+        parts.append((FEED_FORWARDS, layer.feed_forward, layer.prefix + layer.feed_forward_prefix, "feed_forward"))
+    if layer.token_input is not None:
+        parts.append((TOKEN_INPUTS, layer.token_input, layer.prefix + layer.token_input_prefix, "token_input"))
     return parts
 
 
@@ -42,7 +45,12 @@ def expected_tensors(spec: ModelSpec) -> list[TensorSpec]:
             out += registry.get(part.kind).expected_tensors(part, prefix)
     out += NORMS.get(spec.final_norm.kind).expected_tensors(spec.final_norm, spec.final_norm_prefix)
     out.append(TensorSpec(spec.lm_head_name, (spec.vocab_size, spec.hidden_size), optional=spec.tie_word_embeddings))
-    return out
+    unique, seen = [], set()
+    for want in out:  # a tensor several parts share (a table all layers cut their part from) is listed once
+        if want.name not in seen:
+            seen.add(want.name)
+            unique.append(want)
+    return unique
 
 
 class LayeredModel:
@@ -58,8 +66,10 @@ class LayeredModel:
             self.blocks.append(
                 block_cls(
                     build_part(MIXERS, layer.mixer),
-                    build_part(FEED_FORWARDS, layer.feed_forward),
+                    build_part(FEED_FORWARDS, layer.feed_forward) if layer.feed_forward is not None else None,
                     {slot.role: build_part(NORMS, slot.part) for slot in layer.norms},
+                    **({"params": layer.block_params} if layer.block_params else {}),
+                    **({"token_input": build_part(TOKEN_INPUTS, layer.token_input)} if layer.token_input is not None else {}),
                 )
             )
         self.final_norm = build_part(NORMS, spec.final_norm)
@@ -77,7 +87,7 @@ class LayeredModel:
             if entry.cache_from is not None:
                 theirs = self.blocks[self.spec.schedule[owner].layer].mixer.kv_spec()
                 mine = mixer.kv_spec()
-                if theirs is None or mine is None or (theirs.num_kv_heads, theirs.head_dim) != (mine.num_kv_heads, mine.head_dim):
+                if theirs is None or mine is None or (theirs.num_kv_heads, theirs.head_dim, theirs.planes) != (mine.num_kv_heads, mine.head_dim, mine.planes):
                     raise ValueError(f"schedule entry {i} cannot read the cache of entry {owner}: shapes differ")
             needs.append(ExecutionCacheNeed(i, owner, mixer.kv_spec(), mixer.state_spec()))
         return needs
@@ -90,7 +100,8 @@ class LayeredModel:
         self.embedding = tensors[spec.embedding_name].to(device=device, dtype=dtype).contiguous()
         for layer, block in zip(spec.layers, self.blocks):
             for _, _, prefix, role in _layer_parts(layer):
-                part = {"mixer": block.mixer, "feed_forward": block.feed_forward}.get(role) or block.norms[role]
+                part = {"mixer": block.mixer, "feed_forward": block.feed_forward,
+                        "token_input": getattr(block, "token_input", None)}.get(role) or block.norms[role]
                 part.load(tensors, prefix, device, dtype)
         self.final_norm.load(tensors, spec.final_norm_prefix, device, dtype)
         if spec.tie_word_embeddings:
@@ -102,7 +113,7 @@ class LayeredModel:
     def forward(self, ctx, caches: list) -> torch.Tensor:
         """Run the step's tokens through the schedule; returns the float32 stream [T, hidden]."""
         acc = ctx.buffer("stream", (ctx.num_tokens, self.spec.hidden_size), torch.float32)
-        ops.embed(self.embedding, ctx.tokens, acc)
+        ops.embed(self.embedding, ctx.tokens, acc, self.spec.embedding_scale)
         for i, entry in enumerate(self.spec.schedule):
             self.blocks[entry.layer].forward(ctx, acc, caches[i])
         ctx.flush_pending()
@@ -112,3 +123,5 @@ class LayeredModel:
         """Float32 logits of the stream rows ``rows`` (int32) into ``out`` [len(rows), vocab]."""
         x = self.final_norm.apply(ctx, acc, rows=rows, name="final.normed")
         self.lm_head.forward(x, out)
+        if self.spec.logit_scale != 1.0:
+            ops.scale_(out, self.spec.logit_scale)

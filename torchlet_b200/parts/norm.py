@@ -1,5 +1,10 @@
 """RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w, float32 inside
-(v10_triton_paged_gqa/layer/rms_norm.py:7-25, kernel/rms_norm.py:13-22)."""
+(v10_triton_paged_gqa/layer/rms_norm.py:7-25, kernel/rms_norm.py:13-22).
+
+Parameters: ``size``, ``eps``; ``groups`` (default 1): the row is split into that many equal
+consecutive parts and each is divided by its own root mean square, the weight covers the whole
+row; ``weight_name`` (default "weight"): the tensor's name below the norm's prefix ("" when the
+prefix itself is the tensor's name)."""
 from __future__ import annotations
 
 import torch
@@ -15,14 +20,18 @@ class RMSNorm(Norm):
         super().__init__(spec)
         self.size = int(spec.params["size"])
         self.eps = float(spec.params["eps"])
+        self.groups = int(spec.params.get("groups", 1))
+        if self.groups <= 0 or self.size % self.groups:
+            raise ValueError(f"a norm of {self.size} elements cannot be split into {self.groups} equal parts")
         self.weight = None
 
     @classmethod
     def expected_tensors(cls, spec: PartSpec, prefix: str) -> list[TensorSpec]:
-        return [TensorSpec(prefix + "weight", (int(spec.params["size"]),), init="ones")]
+        return [TensorSpec(prefix + spec.params.get("weight_name", "weight"), (int(spec.params["size"]),), init="ones")]
 
     def load(self, tensors: dict, prefix: str, device, dtype) -> None:
-        self.weight = tensors[prefix + "weight"].to(device=device, dtype=torch.float32).contiguous()
+        name = prefix + self.spec.params.get("weight_name", "weight")
+        self.weight = tensors[name].to(device=device, dtype=torch.float32).contiguous()
 
     fuses_pending = True  # a product's unfinished sum into the stream is completed in the norm's own kernel
 
@@ -32,11 +41,11 @@ class RMSNorm(Norm):
         count = acc.shape[0] if rows is None else rows.numel()
         if out is None:
             out = ctx.buffer(name, (count, self.size), ctx.dtype)
-        if rows is None and out.dtype == torch.bfloat16:
+        if rows is None and out.dtype == torch.bfloat16 and self.groups == 1:
             pending = ctx.take_pending(acc)
             if pending is not None:  # finish the sum and norm in one kernel
                 ops.finish_accum_norm(pending.partials, pending.splits, pending.bias, acc, self.weight, self.eps, out)
                 return out
         ctx.flush_pending()
-        ops.rms_norm(acc, self.weight, self.eps, out, rows)
+        ops.rms_norm(acc, self.weight, self.eps, out, rows, self.groups)
         return out

@@ -122,6 +122,12 @@ def read_safetensors(model_dir: str | Path) -> dict:
     return {name: lazy._handle(name).get_tensor(name) for name in lazy}
 
 
+def checkpoint_shapes(model_dir: str | Path) -> dict:
+    """Tensor name -> shape of the folder's checkpoint, from the files' headers alone."""
+    lazy = LazyCheckpoint(_checkpoint_files(Path(model_dir)))
+    return {name: lazy.meta(name)[0] for name in lazy}
+
+
 def check_and_normalise(tensors, expected: list):
     """Check names and shapes against ``expected`` (``TensorSpec`` list); returns the
     tensors with integer tables as int32 (for a ``LazyCheckpoint``: itself, restricted to the

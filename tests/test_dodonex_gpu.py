@@ -51,6 +51,16 @@ def test_portions_of_changing_size(name, dtype, page_size):
         assert torch.equal(got, whole)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_steps_of_many_tokens(dtype):
+    """300 tokens in one step, and 270 behind 30 cached ones: in bfloat16 the per-head products of the
+    latent attention run on the tensor cores from 256 tokens on."""
+    ids, want = cases.plain_logits("R", 300, 11)
+    runner = cases.make_runner("R", dtype)
+    cases.assert_close(cases.replay(runner, "a", ids, [300]), want, dtype, "300 tokens")
+    cases.assert_close(cases.replay(runner, "b", ids, [30, 270]), want, dtype, "270 behind 30")
+
+
 @pytest.mark.parametrize("name", ["P", "R"])
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_unequal_batches_with_pages_and_slots_used_again(name, dtype):

@@ -240,3 +240,68 @@ def test_latent_attention_kernels_against_expanded_keys_and_values(dtype, H, D, 
     row_tol = 1e-5 if dtype == torch.float32 else 1e-2
     assert (cached[:, :rank] - kv[0]).abs().max() <= row_tol * kv[0].abs().max()
     assert (cached[:, rank:] - kv[1]).abs().max() <= row_tol * kv[1].abs().max()
+
+
+@pytest.mark.parametrize("H,rank,rot", [(3, 48, 16), (16, 128, 16), (5, 144, 32), (8, 256, 32), (70, 64, 16), (4, 512, 64)])
+def test_tensor_core_latent_attention_equals_the_plain_kernel(H, rank, rot):
+    """The mma.sync kernel against the one-warp-a-row kernel on the same cache: prompt portions with
+    a cached prefix, single tokens with their keys split over several CTAs, requests of unequal
+    length in one step; pages shuffled, the rest of the pool NaN."""
+    from torchlet_b200 import ops
+
+    dk, page_size = rank + rot, 16
+    assert ops.latent_attention_mma_supported(dk, rank)
+    lens = [(130, 37), (0, 5), (700, 1), (63, 66)]  # (cached before, new tokens)
+    total = sum(b + q for b, q in lens)
+    num_pages = sum(-(-(b + q) // page_size) for b, q in lens) + 3
+    pages = torch.full((num_pages, 1, 1, page_size, dk), float("nan"), device=DEV, dtype=torch.bfloat16)
+    order = (torch.randperm(num_pages - 1, generator=torch.Generator().manual_seed(5)) + 1).tolist()
+    width = max(-(-(b + q) // page_size) for b, q in lens)
+    table = torch.zeros(len(lens), width, dtype=torch.int32)
+    flat = pages.view(num_pages * page_size, dk)
+    for r, (b, q) in enumerate(lens):
+        n = -(-(b + q) // page_size)
+        mine = [order.pop() for _ in range(n)]
+        table[r, :n] = torch.tensor(mine)
+        rows = rand(b + q, dk, seed=60 + r, scale=0.5).bfloat16()
+        index = torch.tensor(mine).repeat_interleave(page_size)[:b + q] * page_size + torch.arange(b + q) % page_size
+        flat[index.to(DEV)] = rows.to(DEV)
+    T = sum(q for _, q in lens)
+    q_abs = rand(T, H * dk, seed=70, scale=0.6).bfloat16().to(DEV)
+    indptr = torch.tensor([0] + torch.tensor([q for _, q in lens]).cumsum(0).tolist(), dtype=torch.int32, device=DEV)
+    before = torch.tensor([b for b, _ in lens], dtype=torch.int32, device=DEV)
+    token_req = torch.cat([torch.full((q,), r, dtype=torch.int32) for r, (_, q) in enumerate(lens)]).to(DEV)
+    positions = torch.cat([torch.arange(b, b + q, dtype=torch.int32) for b, q in lens]).to(DEV)
+    table = table.to(DEV)
+    want = torch.empty(T, H * rank, device=DEV, dtype=torch.bfloat16)
+    ops.latent_attention(q_abs, pages, table, token_req, positions, want, T, H, dk, rank, page_size, 0.2)
+    tile_req, tile_row = [], []
+    for r, (_, q) in enumerate(lens):
+        for row in range(0, q * H, 64):
+            tile_req.append(r)
+            tile_row.append(row)
+    got = torch.full_like(want, float("nan"))
+    ops.latent_attention_mma(q_abs, pages, table, indptr, before, torch.tensor(tile_req, dtype=torch.int32, device=DEV),
+                             torch.tensor(tile_row, dtype=torch.int32, device=DEV), len(tile_req), got, T, H, dk, rank,
+                             page_size, 0.2)
+    assert torch.isfinite(got.float()).all()
+    assert (got.float() - want.float()).abs().max() <= 2e-2 * want.float().abs().max()
+    # single tokens, keys split over CTAs (more splits than some requests have key tiles)
+    singles = [(700, 1), (5, 1), (64, 1), (255, 1)]
+    sel = [0, 1, 3]  # requests of the cache above that are long enough: 167, 5 and 129 tokens hold
+    lens1 = [(lens[0][0] + lens[0][1] - 1, 1), (lens[1][0] + lens[1][1] - 1, 1), (lens[3][0] + lens[3][1] - 1, 1), (700, 1)]
+    reqs = [0, 1, 3, 2]
+    T1 = len(reqs)
+    q1 = rand(T1, H * dk, seed=71, scale=0.6).bfloat16().to(DEV)
+    table1 = table[torch.tensor(reqs, device=DEV)].contiguous()
+    indptr1 = torch.arange(T1 + 1, dtype=torch.int32, device=DEV)
+    before1 = torch.tensor([b for b, _ in lens1], dtype=torch.int32, device=DEV)
+    req1 = torch.arange(T1, dtype=torch.int32, device=DEV)
+    want1 = torch.empty(T1, H * rank, device=DEV, dtype=torch.bfloat16)
+    ops.latent_attention(q1, pages, table1, req1, before1, want1, T1, H, dk, rank, page_size, 0.2)
+    for splits in (1, 3, 16):
+        got1 = torch.full_like(want1, float("nan"))
+        ops.latent_attention_mma(q1, pages, table1, indptr1, before1, None, None, T1 * (-(-H // 64)), got1, T1, H, dk,
+                                 rank, page_size, 0.2, splits)
+        assert torch.isfinite(got1.float()).all(), splits
+        assert (got1.float() - want1.float()).abs().max() <= 2e-2 * want1.float().abs().max(), splits

@@ -12,8 +12,8 @@
 //   prepare  one block per (token, head): w, u and a * u of every key channel;
 //   scan     one WARP per (request, head, 32 value channels): the columns of S are independent
 //            of one another, so a lane keeps one column (D floats) in registers and walks the
-//            request's tokens of this step in order; r, k, w, u, a*u of a few tokens at a time
-//            are staged in shared memory and read as broadcasts.  The state row of the
+//            request's tokens of this step in order; r, k, v, w, u, a*u of a few tokens at a time
+//            are staged in shared memory (two stages, asynchronous copies) and read as broadcasts.  The state row of the
 //            request's slot is read at the start and written back at the end, so a prompt
 //            cut into portions, or decoded token by token, runs the same additions in the
 //            same order as the whole prompt;
@@ -61,16 +61,27 @@ delta_prepare_kernel(const float* __restrict__ proj, int proj_stride, const floa
   out[2 * dim + i] = a * u;
 }
 
-constexpr int CHUNK = 8;  // tokens staged in shared memory at a time
+__device__ __forceinline__ void copy16(void* smem, const void* gmem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void copies_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void copies_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
 
-template <int DK>
+// r, k, v, w, u, a*u of CHUNK tokens are staged in shared memory, two stages deep: while the warp
+// walks one chunk, the next one is on its way (16-byte asynchronous copies where D and the row
+// stride are multiples of 4 floats, plain loads otherwise).
+template <int DK, bool VEC>
 __global__ void __launch_bounds__(32)
 delta_scan_kernel(const float* __restrict__ proj, int proj_stride, const float* __restrict__ gates,
                   const int* __restrict__ req_indptr, const int* __restrict__ slots, float* __restrict__ state,
                   float* __restrict__ out, int heads, int dim, int max_slots) {
   tl::pdl_launch_dependents();
   tl::pdl_wait();
-  __shared__ __align__(16) float stage[CHUNK][5][DK];  // r, k, w, u, a*u
+  constexpr int CHUNK = DK <= 64 ? 8 : (DK <= 128 ? 4 : 2);
+  __shared__ __align__(16) float stage[2][CHUNK][6][DK];  // r, k, v, w, u, a*u
   const int req = blockIdx.x, h = blockIdx.y, lane = threadIdx.x;
   const int j = blockIdx.z * 32 + lane;
   const bool on = j < dim;
@@ -83,35 +94,56 @@ delta_scan_kernel(const float* __restrict__ proj, int proj_stride, const float* 
       for (int t = first; t < last; ++t) out[(size_t)t * hd + h * dim + j] = 0.f;
     return;
   }
+  if (!VEC || dim < DK) {  // entries past dim stay zero in both stages
+    for (int e = lane; e < 2 * CHUNK * 6 * DK; e += 32) (&stage[0][0][0][0])[e] = 0.f;
+    __syncwarp();
+  }
+  auto fetch = [&](int base, int buf) {
+    const int count = last - base < CHUNK ? last - base : CHUNK;
+    if (VEC) {
+      const int quads = dim >> 2;
+      for (int e = lane; e < count * 6 * quads; e += 32) {
+        const int tt = e / (6 * quads), rest = e - tt * 6 * quads, what = rest / quads, q = rest - what * quads;
+        const int t = base + tt;
+        const float* src = what < 3 ? proj + (size_t)t * proj_stride + what * hd + h * dim
+                                    : gates + (((size_t)t * heads + h) * 3 + (what - 3)) * dim;
+        copy16(&stage[buf][tt][what][4 * q], src + 4 * q);
+      }
+    } else {
+      for (int e = lane; e < count * 6 * dim; e += 32) {
+        const int tt = e / (6 * dim), rest = e - tt * 6 * dim, what = rest / dim, i = rest - what * dim;
+        const int t = base + tt;
+        stage[buf][tt][what][i] = what < 3 ? proj[(size_t)t * proj_stride + what * hd + h * dim + i]
+                                           : gates[(((size_t)t * heads + h) * 3 + (what - 3)) * dim + i];
+      }
+    }
+    copies_commit();
+  };
+  if (first < last) fetch(first, 0);
+
   float* mine = state + ((size_t)slot * heads + h) * dim * dim;
   float S[DK];
 #pragma unroll
   for (int i = 0; i < DK; ++i) S[i] = (on && i < dim) ? mine[(size_t)i * dim + j] : 0.f;
 
-  for (int base = first; base < last; base += CHUNK) {
+  int buf = 0;
+  for (int base = first; base < last; base += CHUNK, buf ^= 1) {
     const int count = last - base < CHUNK ? last - base : CHUNK;
-    __syncwarp();
-    for (int e = lane; e < count * 5 * DK; e += 32) {
-      const int tt = e / (5 * DK), rest = e % (5 * DK), what = rest / DK, i = rest % DK;
-      const int t = base + tt;
-      float v = 0.f;
-      if (i < dim) {
-        if (what < 2)
-          v = proj[(size_t)t * proj_stride + what * hd + h * dim + i];
-        else
-          v = gates[(((size_t)t * heads + h) * 3 + (what - 2)) * dim + i];
-      }
-      stage[tt][what][i] = v;
+    if (base + CHUNK < last) {
+      fetch(base + CHUNK, buf ^ 1);
+      copies_wait<1>();
+    } else {
+      copies_wait<0>();
     }
     __syncwarp();
     for (int tt = 0; tt < count; ++tt) {
       const int t = base + tt;
-      const float v = on ? proj[(size_t)t * proj_stride + 2 * hd + h * dim + j] : 0.f;
-      const float4* r4 = reinterpret_cast<const float4*>(stage[tt][0]);
-      const float4* k4 = reinterpret_cast<const float4*>(stage[tt][1]);
-      const float4* w4 = reinterpret_cast<const float4*>(stage[tt][2]);
-      const float4* u4 = reinterpret_cast<const float4*>(stage[tt][3]);
-      const float4* au4 = reinterpret_cast<const float4*>(stage[tt][4]);
+      const float v = on ? stage[buf][tt][2][j & (DK - 1)] : 0.f;
+      const float4* r4 = reinterpret_cast<const float4*>(stage[buf][tt][0]);
+      const float4* k4 = reinterpret_cast<const float4*>(stage[buf][tt][1]);
+      const float4* w4 = reinterpret_cast<const float4*>(stage[buf][tt][3]);
+      const float4* u4 = reinterpret_cast<const float4*>(stage[buf][tt][4]);
+      const float4* au4 = reinterpret_cast<const float4*>(stage[buf][tt][5]);
       float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;  // u^T S_old over key channels i = 0, 1, 2, 3 mod 4
 #pragma unroll
       for (int q = 0; q < DK / 4; ++q) {
@@ -137,6 +169,7 @@ delta_scan_kernel(const float* __restrict__ proj, int proj_stride, const float* 
       }
       if (on) out[(size_t)t * hd + h * dim + j] = (o0 + o1) + (o2 + o3);
     }
+    __syncwarp();  // the stage is free for the chunk after the next
   }
   if (on) {
 #pragma unroll
@@ -200,14 +233,20 @@ int tl_delta_scan(const float* proj, int proj_stride, const float* gates, const 
   if (requests <= 0) return 0;
   if (dim <= 0 || dim > 256 || heads > 65535) return TL_ERR_UNSUPPORTED;
   dim3 grid(requests, heads, (dim + 31) / 32);
-#define TL_SCAN(DK)                                                                                          \
-  tl::launch_kernel(delta_scan_kernel<DK>, grid, 32, 0, stream, proj, proj_stride, gates, req_indptr, slots, \
-                    state, out, heads, dim, max_slots)
-  if (dim <= 16) TL_SCAN(16);
-  else if (dim <= 32) TL_SCAN(32);
-  else if (dim <= 64) TL_SCAN(64);
-  else if (dim <= 128) TL_SCAN(128);
-  else TL_SCAN(256);
+  const bool vec = dim % 4 == 0 && proj_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(proj) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(gates) & 15) == 0;
+#define TL_SCAN(DK)                                                                                                \
+  if (vec)                                                                                                         \
+    tl::launch_kernel(delta_scan_kernel<DK, true>, grid, 32, 0, stream, proj, proj_stride, gates, req_indptr,      \
+                      slots, state, out, heads, dim, max_slots);                                                   \
+  else                                                                                                             \
+    tl::launch_kernel(delta_scan_kernel<DK, false>, grid, 32, 0, stream, proj, proj_stride, gates, req_indptr,     \
+                      slots, state, out, heads, dim, max_slots)
+  if (dim <= 16) { TL_SCAN(16); }
+  else if (dim <= 32) { TL_SCAN(32); }
+  else if (dim <= 64) { TL_SCAN(64); }
+  else if (dim <= 128) { TL_SCAN(128); }
+  else { TL_SCAN(256); }
 #undef TL_SCAN
   return TL_LAUNCH_CHECK();
 }

@@ -11,12 +11,13 @@
 //   prepare     one block per token: RMS norm of the query latent (-> compute type), RMS norm
 //               of the key/value latent and rotation of the shared key part, both written into
 //               the token's cache row; float32 inside;
-//   absorb_q    one block per (token, head): rotate q_rot; fold W_uk,h into q_plain;
+//   absorb_q    one block per (8 tokens, head): rotate q_rot; fold W_uk,h into q_plain;
 //   attention   one warp per (token, head), keys in tiles of 32 consecutive ABSOLUTE positions,
 //               float32 scores, online softmax and sums: the order of every sum depends only on
 //               the token's position, never on the cut, the batch or the pages (the true 32-bit
 //               kernel and the any-size kernel);
-//   expand_o    one block per (token, head): out[t, h] = W_uv,h o_lat[t, h].
+//   expand_o    one block per (8 tokens, head): out[t, h] = W_uv,h o_lat[t, h].
+// For many tokens the two per-head products run on the tensor cores instead (the mixer's choice).
 //
 // Rotation: entry i of the first ``dims`` entries pairs with i + dims/2, angle = float(p) *
 // inv_freq[i] in float32; entries past ``dims`` pass unchanged.
@@ -76,38 +77,59 @@ latent_prepare_kernel(const float* __restrict__ down, int down_stride, int q_ran
 }
 
 // q: float32 [T, heads * (dim + rot_dim)];  uk: T [heads * dim, kv_rank];
-// q_abs: T [T, heads, kv_rank + rot_dim].
+// q_abs: T [T, heads, kv_rank + rot_dim].  A block takes up to TOKENS tokens of one head, so that a
+// weight is read once for all of them.  ``fold`` 0: only the rotated part is written (the folded
+// part comes from a tensor-core product) and ``plain_out`` (optional) receives q_plain in T.
+constexpr int TOKENS = 8;
+
 template <typename T, int NT>
 __global__ void __launch_bounds__(NT)
 latent_absorb_q_kernel(const float* __restrict__ q, int q_stride, const T* __restrict__ uk,
                        const float* __restrict__ inv_freq, const int* __restrict__ positions, T* __restrict__ q_abs,
-                       int heads, int dim, int rot_dim, int rot_dims, int kv_rank) {
+                       T* __restrict__ plain_out, int tokens, int heads, int dim, int rot_dim, int rot_dims,
+                       int kv_rank, int fold) {
   tl::pdl_launch_dependents();
   tl::pdl_wait();
-  extern __shared__ float plain[];  // dim floats
-  const int t = blockIdx.x, h = blockIdx.y;
-  const float* row = q + (size_t)t * q_stride + (size_t)h * (dim + rot_dim);
-  for (int i = threadIdx.x; i < dim; i += NT) plain[i] = row[i];
-  __syncthreads();
-  T* out = q_abs + ((size_t)t * heads + h) * (kv_rank + rot_dim);
-  const T* w = uk + (size_t)h * dim * kv_rank;
-  for (int r = threadIdx.x; r < kv_rank; r += NT) {
-    float sum = 0.f;
-    for (int d = 0; d < dim; ++d) sum = fmaf(plain[d], to_float(w[(size_t)d * kv_rank + r]), sum);
-    out[r] = from_float<T>(sum);
+  extern __shared__ float plain[];  // TOKENS x dim floats
+  const int t0 = blockIdx.x * TOKENS, h = blockIdx.y;
+  const int count = tokens - t0 < TOKENS ? tokens - t0 : TOKENS;
+  for (int e = threadIdx.x; e < TOKENS * dim; e += NT) {
+    const int tt = e / dim, i = e - tt * dim;
+    const float v = tt < count ? q[(size_t)(t0 + tt) * q_stride + (size_t)h * (dim + rot_dim) + i] : 0.f;
+    plain[e] = v;
+    if (plain_out && tt < count) plain_out[((size_t)(t0 + tt) * heads + h) * dim + i] = from_float<T>(v);
   }
-  const float* qr = row + dim;
+  __syncthreads();
+  const int row = kv_rank + rot_dim;
+  if (fold) {
+    const T* w = uk + (size_t)h * dim * kv_rank;
+    for (int r = threadIdx.x; r < kv_rank; r += NT) {
+      float sum[TOKENS];
+#pragma unroll
+      for (int tt = 0; tt < TOKENS; ++tt) sum[tt] = 0.f;
+#pragma unroll 4
+      for (int d = 0; d < dim; ++d) {
+        const float wv = to_float(w[(size_t)d * kv_rank + r]);
+#pragma unroll
+        for (int tt = 0; tt < TOKENS; ++tt) sum[tt] = fmaf(plain[tt * dim + d], wv, sum[tt]);
+      }
+#pragma unroll
+      for (int tt = 0; tt < TOKENS; ++tt)
+        if (tt < count) q_abs[((size_t)(t0 + tt) * heads + h) * row + r] = from_float<T>(sum[tt]);
+    }
+  }
   const int half = rot_dims / 2;
-  const int pos = positions[t];
-  for (int i = threadIdx.x; i < rot_dim; i += NT) {
+  for (int e = threadIdx.x; e < count * rot_dim; e += NT) {
+    const int tt = e / rot_dim, i = e - tt * rot_dim;
+    const float* qr = q + (size_t)(t0 + tt) * q_stride + (size_t)h * (dim + rot_dim) + dim;
     float v = qr[i];
     if (i < rot_dims) {
       const int f = i < half ? i : i - half;
-      float s, c;
-      sincosf((float)pos * inv_freq[f], &s, &c);
-      v = i < half ? qr[i] * c - qr[i + half] * s : qr[i] * c + qr[i - half] * s;
+      float sn, cs;
+      sincosf((float)positions[t0 + tt] * inv_freq[f], &sn, &cs);
+      v = i < half ? qr[i] * cs - qr[i + half] * sn : qr[i] * cs + qr[i - half] * sn;
     }
-    out[kv_rank + i] = from_float<T>(v);
+    q_abs[((size_t)(t0 + tt) * heads + h) * row + kv_rank + i] = from_float<T>(v);
   }
 }
 
@@ -192,24 +214,51 @@ latent_attention_kernel(const T* __restrict__ q_abs, const T* __restrict__ pages
 }
 
 // o_lat: T [T, heads, kv_rank];  uv: T [heads * vdim, kv_rank];  out: T [T, heads * vdim].
-template <typename T>
-__global__ void __launch_bounds__(WARPS * 32)
-latent_expand_o_kernel(const T* __restrict__ o_lat, const T* __restrict__ uv, T* __restrict__ out, int heads,
-                       int vdim, int kv_rank) {
+// A block takes up to TOKENS tokens of one head; a warp a value channel at a time, lanes over
+// the latent (8 consecutive entries a load where kv_rank is a multiple of 8).
+constexpr int EXPAND_WARPS = 8;
+
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(EXPAND_WARPS * 32)
+latent_expand_o_kernel(const T* __restrict__ o_lat, const T* __restrict__ uv, T* __restrict__ out, int tokens,
+                       int heads, int vdim, int kv_rank) {
   tl::pdl_launch_dependents();
   tl::pdl_wait();
-  extern __shared__ float latent[];  // kv_rank floats
-  const int t = blockIdx.x, h = blockIdx.y;
+  extern __shared__ float latent[];  // TOKENS x kv_rank floats
+  const int t0 = blockIdx.x * TOKENS, h = blockIdx.y;
+  const int count = tokens - t0 < TOKENS ? tokens - t0 : TOKENS;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const T* row = o_lat + ((size_t)t * heads + h) * kv_rank;
-  for (int i = threadIdx.x; i < kv_rank; i += WARPS * 32) latent[i] = to_float(row[i]);
+  for (int e = threadIdx.x; e < TOKENS * kv_rank; e += EXPAND_WARPS * 32) {
+    const int tt = e / kv_rank, i = e - tt * kv_rank;
+    latent[e] = tt < count ? to_float(o_lat[((size_t)(t0 + tt) * heads + h) * kv_rank + i]) : 0.f;
+  }
   __syncthreads();
-  for (int v = warp; v < vdim; v += WARPS) {
+  for (int v = warp; v < vdim; v += EXPAND_WARPS) {
     const T* w = uv + ((size_t)h * vdim + v) * kv_rank;
-    float sum = 0.f;
-    for (int r = lane; r < kv_rank; r += 32) sum = fmaf(latent[r], to_float(w[r]), sum);
-    sum = warp_sum(sum);
-    if (lane == 0) out[(size_t)t * heads * vdim + (size_t)h * vdim + v] = from_float<T>(sum);
+    float sum[TOKENS];
+#pragma unroll
+    for (int tt = 0; tt < TOKENS; ++tt) sum[tt] = 0.f;
+    if (VEC) {
+      for (int r = lane * 8; r < kv_rank; r += 256) {
+        float wv[8];
+        load8(w + r, wv);
+#pragma unroll
+        for (int tt = 0; tt < TOKENS; ++tt)
+#pragma unroll
+          for (int j = 0; j < 8; ++j) sum[tt] = fmaf(latent[tt * kv_rank + r + j], wv[j], sum[tt]);
+      }
+    } else {
+      for (int r = lane; r < kv_rank; r += 32) {
+        const float wv = to_float(w[r]);
+#pragma unroll
+        for (int tt = 0; tt < TOKENS; ++tt) sum[tt] = fmaf(latent[tt * kv_rank + r], wv, sum[tt]);
+      }
+    }
+#pragma unroll
+    for (int tt = 0; tt < TOKENS; ++tt) {
+      const float total = warp_sum(sum[tt]);
+      if (lane == 0 && tt < count) out[(size_t)(t0 + tt) * heads * vdim + (size_t)h * vdim + v] = from_float<T>(total);
+    }
   }
 }
 
@@ -238,19 +287,20 @@ int tl_latent_prepare(const float* down, int down_stride, int q_rank, int kv_ran
 }
 
 int tl_latent_absorb_q(const float* q, int q_stride, const void* uk, int dtype, const float* inv_freq,
-                       const int* positions, void* q_abs, int tokens, int heads, int dim, int rot_dim, int rot_dims,
-                       int kv_rank, cudaStream_t stream) {
+                       const int* positions, void* q_abs, void* plain_out, int tokens, int heads, int dim, int rot_dim,
+                       int rot_dims, int kv_rank, int fold, cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (heads > 65535 || rot_dims % 2 || rot_dims > rot_dim) return TL_ERR_UNSUPPORTED;
-  dim3 grid(tokens, heads);
-  const size_t smem = (size_t)dim * sizeof(float);
+  if (heads > 65535 || rot_dims % 2 || rot_dims > rot_dim || dim > 1024) return TL_ERR_UNSUPPORTED;
+  dim3 grid((tokens + TOKENS - 1) / TOKENS, heads);
+  const size_t smem = (size_t)TOKENS * dim * sizeof(float);
   if (dtype == TL_DTYPE_F32)
-    tl::launch_kernel(latent_absorb_q_kernel<float, 128>, grid, 128, smem, stream, q, q_stride, (const float*)uk,
-                      inv_freq, positions, (float*)q_abs, heads, dim, rot_dim, rot_dims, kv_rank);
+    tl::launch_kernel(latent_absorb_q_kernel<float, 256>, grid, 256, smem, stream, q, q_stride, (const float*)uk,
+                      inv_freq, positions, (float*)q_abs, (float*)plain_out, tokens, heads, dim, rot_dim, rot_dims,
+                      kv_rank, fold);
   else
-    tl::launch_kernel(latent_absorb_q_kernel<__nv_bfloat16, 128>, grid, 128, smem, stream, q, q_stride,
-                      (const __nv_bfloat16*)uk, inv_freq, positions, (__nv_bfloat16*)q_abs, heads, dim, rot_dim,
-                      rot_dims, kv_rank);
+    tl::launch_kernel(latent_absorb_q_kernel<__nv_bfloat16, 256>, grid, 256, smem, stream, q, q_stride,
+                      (const __nv_bfloat16*)uk, inv_freq, positions, (__nv_bfloat16*)q_abs, (__nv_bfloat16*)plain_out,
+                      tokens, heads, dim, rot_dim, rot_dims, kv_rank, fold);
   return TL_LAUNCH_CHECK();
 }
 
@@ -279,15 +329,19 @@ int tl_latent_attention(const void* q_abs, const void* pages, int dtype, const i
 int tl_latent_expand_o(const void* o_lat, const void* uv, void* out, int dtype, int tokens, int heads, int vdim,
                        int kv_rank, cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (heads > 65535) return TL_ERR_UNSUPPORTED;
-  dim3 grid(tokens, heads);
-  const size_t smem = (size_t)kv_rank * sizeof(float);
-  if (dtype == TL_DTYPE_F32)
-    tl::launch_kernel(latent_expand_o_kernel<float>, grid, WARPS * 32, smem, stream, (const float*)o_lat,
-                      (const float*)uv, (float*)out, heads, vdim, kv_rank);
-  else
-    tl::launch_kernel(latent_expand_o_kernel<__nv_bfloat16>, grid, WARPS * 32, smem, stream,
-                      (const __nv_bfloat16*)o_lat, (const __nv_bfloat16*)uv, (__nv_bfloat16*)out, heads, vdim, kv_rank);
+  if (heads > 65535 || kv_rank > 1024) return TL_ERR_UNSUPPORTED;
+  dim3 grid((tokens + TOKENS - 1) / TOKENS, heads);
+  const size_t smem = (size_t)TOKENS * kv_rank * sizeof(float);
+  const bool vec = kv_rank % 8 == 0;
+#define TL_EXPAND(T, VEC)                                                                                          \
+  tl::launch_kernel(latent_expand_o_kernel<T, VEC>, grid, EXPAND_WARPS * 32, smem, stream, (const T*)o_lat,        \
+                    (const T*)uv, (T*)out, tokens, heads, vdim, kv_rank)
+  if (dtype == TL_DTYPE_F32) {
+    if (vec) TL_EXPAND(float, true); else TL_EXPAND(float, false);
+  } else {
+    if (vec) TL_EXPAND(__nv_bfloat16, true); else TL_EXPAND(__nv_bfloat16, false);
+  }
+#undef TL_EXPAND
   return TL_LAUNCH_CHECK();
 }
 

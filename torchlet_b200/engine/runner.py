@@ -550,7 +550,7 @@ class ModelRunner:
         width = max(1, max(-(-(b + q) // cache.page_size) for b, q in zip(kv_before, lens)))
         G = self.num_groups
         words = 3 * T + (n + 1) + 2 * n + m + G * n * width + (4 * k + 2 if hot else 0)
-        host, dev = self._meta(words + T + 4 * n + 1024)  # room for what parts plan on the host
+        host, dev = self._meta(words + 5 * T + 8 * n + 4096)  # room for what parts plan on the host (row tiles)
         self._aux_offset = words
         o = 0
 

@@ -109,12 +109,19 @@ _SIGNATURES = {
         "tl_latent_prepare": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_float,
                               c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_int,
                               c_int, c_void_p],
-        "tl_latent_absorb_q": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                               c_int, c_int, c_int, c_void_p],
+        "tl_latent_absorb_q": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                               c_int, c_int, c_int, c_int, c_int, c_void_p],
         "tl_latent_attention": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                 c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
         "tl_latent_expand_o": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "tl_latent_attention_debug_error": [c_void_p],
+    },
+    "latent_attention_mma": {
+        "tl_latent_attention_mma_supported": [c_int, c_int],
+        "tl_latent_attention_mma": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                    c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p,
+                                    c_void_p, c_void_p],
+        "tl_latent_attention_mma_debug_error": [c_void_p],
     },
     "sampling": {
         "tl_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -398,16 +405,21 @@ def latent_prepare(down, q_rank, kv_rank, rot_dim, rot_dims, q_norm, kv_norm, in
     _check(code, "latent_prepare")
 
 
-def latent_absorb_q(q, uk, inv_freq, positions, q_abs, heads, dim, rot_dim, rot_dims, kv_rank) -> None:
-    """q float32 [T, H (dim + rot)] -> q_abs [T, H, kv_rank + rot]: W_uk,h^T q_plain and the rotated part."""
-    _need_cuda(q, uk, inv_freq, positions, q_abs)
+def latent_absorb_q(q, uk, inv_freq, positions, q_abs, heads, dim, rot_dim, rot_dims, kv_rank, fold: bool = True,
+                    plain_out=None) -> None:
+    """q float32 [T, H (dim + rot)] -> q_abs [T, H, kv_rank + rot]: W_uk,h^T q_plain and the rotated part.
+    ``fold`` False: only the rotated part is written (the folded part comes from a tensor-core product of
+    ``plain_out``, which receives q_plain [T, H dim] in the compute type)."""
+    _need_cuda(q, uk, inv_freq, positions, q_abs, plain_out)
     tokens = q.shape[0]
     assert q.dtype == torch.float32 and q.stride(1) == 1 and q.shape[1] == heads * (dim + rot_dim)
     assert uk.dtype == q_abs.dtype and uk.is_contiguous() and uk.shape == (heads * dim, kv_rank)
     assert q_abs.is_contiguous() and q_abs.numel() == tokens * heads * (kv_rank + rot_dim)
+    assert plain_out is None or (plain_out.dtype == q_abs.dtype and plain_out.is_contiguous()
+                                 and plain_out.numel() == tokens * heads * dim)
     code = _fn("latent_attention", "tl_latent_absorb_q")(
         q.data_ptr(), q.stride(0), uk.data_ptr(), dtype_code(uk.dtype), inv_freq.data_ptr(), positions.data_ptr(),
-        q_abs.data_ptr(), tokens, heads, dim, rot_dim, rot_dims, kv_rank, _stream())
+        q_abs.data_ptr(), _ptr(plain_out), tokens, heads, dim, rot_dim, rot_dims, kv_rank, 1 if fold else 0, _stream())
     _check(code, "latent_absorb_q")
 
 
@@ -423,6 +435,32 @@ def latent_attention(q_abs, pages, block_table, token_req, positions, out, token
         token_req.data_ptr(), positions.data_ptr(), out.data_ptr(), tokens, heads, dk, dv, page_size, float(scale),
         pages.shape[0], _stream())
     _check(code, "latent_attention")
+
+
+def latent_attention_mma_supported(dk: int, dv: int) -> bool:
+    """Sizes the tensor-core latent attention takes (multiples of 16, value size up to 512)."""
+    return bool(_fn("latent_attention_mma", "tl_latent_attention_mma_supported")(dk, dv))
+
+
+def latent_attention_mma(q_abs, pages, block_table, req_indptr, kv_before, tile_req, tile_row, tiles, out, tokens,
+                         heads, dk, dv, page_size, scale, splits: int = 1) -> None:
+    """Latent-space attention on the tensor cores (csrc/latent_attention_mma.cu), bfloat16.  Row tiles
+    of 64 packed (token, head) rows: ``tile_req``/``tile_row`` name each tile's request and first row,
+    or are None when every request brings one token.  ``splits`` > 1 (single tokens only): that many
+    CTAs share a request's keys and a second kernel merges them."""
+    _need_cuda(q_abs, pages, block_table, req_indptr, kv_before, tile_req, tile_row, out)
+    assert q_abs.dtype == pages.dtype == out.dtype == torch.bfloat16
+    assert q_abs.is_contiguous() and out.is_contiguous() and pages.is_contiguous()
+    part_o = part_ml = None
+    if splits > 1:
+        rows = tokens * heads
+        ws = _workspace(("latent_attention", q_abs.device), rows * splits * (dv + 2) * 4)
+        part_o, part_ml = ws, ws[rows * splits * dv:]
+    code = _fn("latent_attention_mma", "tl_latent_attention_mma")(
+        q_abs.data_ptr(), pages.data_ptr(), block_table.data_ptr(), block_table.shape[1], req_indptr.data_ptr(),
+        kv_before.data_ptr(), _ptr(tile_req), _ptr(tile_row), tiles, out.data_ptr(), tokens, heads, dk, dv, page_size,
+        float(scale), pages.shape[0], splits, _ptr(part_o), _ptr(part_ml), _stream())
+    _check(code, "latent_attention_mma", 2 if splits > 1 else 1)
 
 
 def latent_expand_o(o_lat, uv, out, heads, vdim, kv_rank) -> None:
@@ -711,7 +749,7 @@ def debug_errors() -> list:
     in the ordinary build (``TORCHLET_B200_DEBUG`` unset), whose kernels carry no checks."""
     found = []
     for library in ("elementwise", "attention_generic", "attention_mma", "decode_fused", "slots", "stream_ops",
-                    "delta_rule", "latent_attention"):
+                    "delta_rule", "latent_attention", "latent_attention_mma"):
         if any(name in _functions for name in _SIGNATURES[library]):
             value = ctypes.c_int(0)
             code = _fn(library, f"tl_{library}_debug_error")(ctypes.byref(value))

@@ -18,12 +18,53 @@ uk, uv, o.
 """
 from __future__ import annotations
 
+import functools
+
+import numpy as np
 import torch
 
 from .. import ops
 from ..config.spec import PartSpec
 from .base import MIXERS, KVSpec, Mixer, TensorSpec
 from .linear import Linear
+
+
+ROWS = 64  # packed (token, head) rows of a tile, as in csrc/latent_attention_mma.cu
+MIN_KEYS_A_SPLIT = 128
+MIN_TOKENS_FOR_HEAD_PRODUCTS = 256  # below: one kernel for all heads on the CUDA cores (a launch a head costs more)
+
+
+@functools.lru_cache(maxsize=None)
+def _sm_count(device_index: int) -> int:
+    return torch.cuda.get_device_properties(device_index).multi_processor_count
+
+
+def row_tiles(ctx, heads: int):
+    """The row tiles of a step for the tensor-core kernel: (tile_req, tile_row, tiles, key splits),
+    planned once a step for every layer with the same number of heads.  A step of single tokens
+    plans nothing on the host (tile i is request i's) and splits each request's keys over as many
+    CTAs as fill the GPU once, given the longest request the step may meet; the kernel decides on
+    the device how many key tiles a split really has."""
+    key = ("latent_attention.tiles", heads)
+    plan = ctx.plans.get(key)
+    if plan is None:
+        if ctx.decode_only:
+            tiles = ctx.num_requests * (-(-heads // ROWS))
+            room = max(1, 2 * _sm_count(torch.cuda.current_device()) // tiles)
+            splits = max(1, min(room, -(-ctx.max_kv_len // MIN_KEYS_A_SPLIT), 64))
+            plan = (None, None, tiles, splits)
+        else:
+            indptr = ctx.req_indptr_host
+            tile_req, tile_row = [], []
+            for r in range(ctx.num_requests):
+                rows = int(indptr[r + 1] - indptr[r]) * heads
+                for row in range(0, rows, ROWS):
+                    tile_req.append(r)
+                    tile_row.append(row)
+            both = ctx.upload(np.asarray(tile_req + tile_row, dtype=np.int32))
+            plan = (both[:len(tile_req)], both[len(tile_req):], len(tile_req), 1)
+        ctx.plans[key] = plan
+    return plan
 
 
 @MIXERS.register("latent_attention")
@@ -52,7 +93,7 @@ class LatentAttentionMixer(Mixer):
         self.down_proj: Linear | None = None
         self.uq_proj: Linear | None = None
         self.o_proj: Linear | None = None
-        self.uk = self.uv = self.q_norm = self.kv_norm = self.inv_freq = None
+        self.uk = self.uv = self.uk_heads = self.q_norm = self.kv_norm = self.inv_freq = None
 
     def kv_spec(self) -> KVSpec:
         return KVSpec(1, self.row, None, planes=1)
@@ -79,6 +120,12 @@ class LatentAttentionMixer(Mixer):
         self.o_proj = Linear(tensors[prefix + "o"], None, device, dtype)
         self.uk = tensors[prefix + "uk"].to(device=device, dtype=dtype).contiguous()
         self.uv = tensors[prefix + "uv"].to(device=device, dtype=dtype).contiguous()
+        # for steps of many tokens in bfloat16: W_uk,h^T as a [kv_rank, dim] matrix a head, the operand
+        # layout of the tensor-core product (sizes it takes: everything a multiple of 8)
+        self.uk_heads = None
+        sizes = (self.head_dim, self.kv_rank, self.rot_dim, self.v_dim)
+        if dtype == torch.bfloat16 and all(n % 8 == 0 for n in sizes):
+            self.uk_heads = self.uk.view(self.num_heads, self.head_dim, self.kv_rank).transpose(1, 2).contiguous()
         f32 = lambda name: tensors[prefix + name].to(device=device, dtype=torch.float32).contiguous()
         self.q_norm = f32("dq.norm")
         self.kv_norm = f32("dkv.norm") if self.own_kv else None
@@ -99,12 +146,34 @@ class LatentAttentionMixer(Mixer):
         q = ctx.buffer("latent.q", (tokens, H * (self.head_dim + self.rot_dim)), torch.float32)
         self.uq_proj.forward(c_q, q)
         q_abs = ctx.buffer("latent.q_abs", (tokens, H * self.row), ctx.dtype)
-        ops.latent_absorb_q(q, self.uk, self.inv_freq, ctx.positions, q_abs, H, self.head_dim, self.rot_dim,
-                            self.rot_dims, self.kv_rank)
+        per_head_products = self.uk_heads is not None and tokens >= MIN_TOKENS_FOR_HEAD_PRODUCTS
+        if per_head_products:  # many tokens: W_uk,h^T q_plain[h] of every head on the tensor cores
+            D, rank = self.head_dim, self.kv_rank
+            plain = ctx.buffer("latent.q_plain", (tokens, H * D), ctx.dtype)
+            ops.latent_absorb_q(q, self.uk, self.inv_freq, ctx.positions, q_abs, H, D, self.rot_dim, self.rot_dims,
+                                rank, fold=False, plain_out=plain)
+            for h in range(H):
+                ops.gemm_tc(plain[:, h * D:(h + 1) * D], self.uk_heads[h], q_abs[:, h * self.row:h * self.row + rank],
+                            None, ops.EPI_STORE_BF16)
+        else:
+            ops.latent_absorb_q(q, self.uk, self.inv_freq, ctx.positions, q_abs, H, self.head_dim, self.rot_dim,
+                                self.rot_dims, self.kv_rank)
         o_lat = ctx.buffer("latent.o_lat", (tokens, H * self.kv_rank), ctx.dtype)
-        ops.latent_attention(q_abs, cache.pages, cache.block_table, ctx.token_req, ctx.positions, o_lat, tokens, H,
-                             self.row, self.kv_rank, cache.page_size, self.scale)
+        if ctx.dtype == torch.bfloat16 and ops.latent_attention_mma_supported(self.row, self.kv_rank):
+            tile_req, tile_row, tiles, splits = row_tiles(ctx, H)
+            ops.latent_attention_mma(q_abs, cache.pages, cache.block_table, ctx.req_indptr, ctx.kv_before, tile_req,
+                                     tile_row, tiles, o_lat, tokens, H, self.row, self.kv_rank, cache.page_size,
+                                     self.scale, splits)
+        else:
+            ops.latent_attention(q_abs, cache.pages, cache.block_table, ctx.token_req, ctx.positions, o_lat, tokens, H,
+                                 self.row, self.kv_rank, cache.page_size, self.scale)
         out = ctx.buffer("latent.out", (tokens, H * self.v_dim), ctx.dtype)
-        ops.latent_expand_o(o_lat, self.uv, out, H, self.v_dim, self.kv_rank)
+        if per_head_products:
+            V, rank = self.v_dim, self.kv_rank
+            for h in range(H):
+                ops.gemm_tc(o_lat[:, h * rank:(h + 1) * rank], self.uv[h * V:(h + 1) * V], out[:, h * V:(h + 1) * V],
+                            None, ops.EPI_STORE_BF16)
+        else:
+            ops.latent_expand_o(o_lat, self.uv, out, H, self.v_dim, self.kv_rank)
         if not self.o_proj.accumulate_later(ctx, out, acc):
             self.o_proj.forward(out, acc, accumulate=True)

@@ -118,7 +118,7 @@ def test_delta_rule_kernels_carry_the_state(H, D, rank):
         proj = rows @ fused.T
         T = rows.shape[0]
         gates = torch.empty(T, H * 3 * D, device=DEV)
-        ops.delta_prepare(proj, f32("w2"), f32("w0"), f32("a.b"), gates, H, D, rank)
+        ops.delta_prepare(proj, f32("w2").t().contiguous(), f32("w0"), f32("a.b"), gates, H, D, rank)
         indptr = torch.tensor([0] + list(torch.tensor([h.shape[0] for _, h in parts]).cumsum(0)), dtype=torch.int32,
                               device=DEV)
         slots = torch.tensor([s for s, _ in parts], dtype=torch.int32, device=DEV)

@@ -97,13 +97,13 @@ latent_absorb_q_kernel(const float* __restrict__ q, int q_stride, const T* __res
     const int tt = e / dim, i = e - tt * dim;
     const float v = tt < count ? q[(size_t)(t0 + tt) * q_stride + (size_t)h * (dim + rot_dim) + i] : 0.f;
     plain[e] = v;
-    if (plain_out && tt < count) plain_out[((size_t)(t0 + tt) * heads + h) * dim + i] = from_float<T>(v);
+    if (plain_out && tt < count && blockIdx.z == 0) plain_out[((size_t)(t0 + tt) * heads + h) * dim + i] = from_float<T>(v);
   }
   __syncthreads();
   const int row = kv_rank + rot_dim;
   if (fold) {
     const T* w = uk + (size_t)h * dim * kv_rank;
-    for (int r = threadIdx.x; r < kv_rank; r += NT) {
+    for (int r = blockIdx.z * NT + threadIdx.x; r < kv_rank; r += NT * gridDim.z) {
       float sum[TOKENS];
 #pragma unroll
       for (int tt = 0; tt < TOKENS; ++tt) sum[tt] = 0.f;
@@ -118,6 +118,7 @@ latent_absorb_q_kernel(const float* __restrict__ q, int q_stride, const T* __res
         if (tt < count) q_abs[((size_t)(t0 + tt) * heads + h) * row + r] = from_float<T>(sum[tt]);
     }
   }
+  if (blockIdx.z) return;
   const int half = rot_dims / 2;
   for (int e = threadIdx.x; e < count * rot_dim; e += NT) {
     const int tt = e / rot_dim, i = e - tt * rot_dim;
@@ -233,7 +234,7 @@ latent_expand_o_kernel(const T* __restrict__ o_lat, const T* __restrict__ uv, T*
     latent[e] = tt < count ? to_float(o_lat[((size_t)(t0 + tt) * heads + h) * kv_rank + i]) : 0.f;
   }
   __syncthreads();
-  for (int v = warp; v < vdim; v += EXPAND_WARPS) {
+  for (int v = blockIdx.z * EXPAND_WARPS + warp; v < vdim; v += EXPAND_WARPS * gridDim.z) {
     const T* w = uv + ((size_t)h * vdim + v) * kv_rank;
     float sum[TOKENS];
 #pragma unroll
@@ -291,8 +292,23 @@ int tl_latent_absorb_q(const float* q, int q_stride, const void* uk, int dtype, 
                        int rot_dims, int kv_rank, int fold, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (heads > 65535 || rot_dims % 2 || rot_dims > rot_dim || dim > 1024) return TL_ERR_UNSUPPORTED;
-  dim3 grid((tokens + TOKENS - 1) / TOKENS, heads);
+  // few tokens: the folded entries of a head are spread over several blocks, so that the weights stream through
+  // many SMs (64 entries a block); many tokens: the grid is large anyway
+  const int chunks = (tokens + TOKENS - 1) / TOKENS;
+  const int parts = (fold && chunks * heads < 256) ? (kv_rank + 63) / 64 : 1;
+  dim3 grid(chunks, heads, parts);
   const size_t smem = (size_t)TOKENS * dim * sizeof(float);
+  if (parts > 1) {
+    if (dtype == TL_DTYPE_F32)
+      tl::launch_kernel(latent_absorb_q_kernel<float, 64>, grid, 64, smem, stream, q, q_stride, (const float*)uk,
+                        inv_freq, positions, (float*)q_abs, (float*)plain_out, tokens, heads, dim, rot_dim, rot_dims,
+                        kv_rank, fold);
+    else
+      tl::launch_kernel(latent_absorb_q_kernel<__nv_bfloat16, 64>, grid, 64, smem, stream, q, q_stride,
+                        (const __nv_bfloat16*)uk, inv_freq, positions, (__nv_bfloat16*)q_abs,
+                        (__nv_bfloat16*)plain_out, tokens, heads, dim, rot_dim, rot_dims, kv_rank, fold);
+    return TL_LAUNCH_CHECK();
+  }
   if (dtype == TL_DTYPE_F32)
     tl::launch_kernel(latent_absorb_q_kernel<float, 256>, grid, 256, smem, stream, q, q_stride, (const float*)uk,
                       inv_freq, positions, (float*)q_abs, (float*)plain_out, tokens, heads, dim, rot_dim, rot_dims,
@@ -330,7 +346,9 @@ int tl_latent_expand_o(const void* o_lat, const void* uv, void* out, int dtype, 
                        int kv_rank, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (heads > 65535 || kv_rank > 1024) return TL_ERR_UNSUPPORTED;
-  dim3 grid((tokens + TOKENS - 1) / TOKENS, heads);
+  const int chunks = (tokens + TOKENS - 1) / TOKENS;
+  const int parts = chunks * heads < 256 ? (vdim + EXPAND_WARPS - 1) / EXPAND_WARPS : 1;  // few tokens: a warp a channel
+  dim3 grid(chunks, heads, parts);
   const size_t smem = (size_t)TOKENS * kv_rank * sizeof(float);
   const bool vec = kv_rank % 8 == 0;
 #define TL_EXPAND(T, VEC)                                                                                          \

@@ -293,28 +293,37 @@ latent_attention_mma_kernel(const Args a) {
   }
 }
 
-// One warp per packed row: out = sum_s e^(m_s - M) O_s / sum_s e^(m_s - M) l_s.
+// One block per packed row: out = sum_s e^(m_s - M) O_s / sum_s e^(m_s - M) l_s.  The splits' weights
+// are taken once (a thread a split), the columns run over the threads.
+constexpr int MAX_SPLITS = 64;
+
 __global__ void __launch_bounds__(128)
 latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out,
-                    long long rows, int splits, int dv) {
+                    int splits, int dv) {
   tl::pdl_wait();
   tl::pdl_launch_dependents();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long row = (long long)blockIdx.x * 4 + warp;
-  if (row >= rows) return;
-  const float* ml = part_ml + (size_t)row * splits * 2;
-  float M = -INFINITY;
-  for (int s = 0; s < splits; ++s) M = fmaxf(M, ml[2 * s]);
-  float l = 0.f;
-  for (int s = 0; s < splits; ++s) l += ml[2 * s] == -INFINITY ? 0.f : expf(ml[2 * s] - M) * ml[2 * s + 1];
-  const float inv = l > 0.f ? 1.f / l : 0.f;
-  for (int c = lane; c < dv; c += 32) {
+  __shared__ float weight[MAX_SPLITS];
+  __shared__ float inv_l;
+  const size_t row = blockIdx.x;
+  const float* ml = part_ml + row * splits * 2;
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    float m0 = lane < splits ? ml[2 * lane] : -INFINITY, m1 = lane + 32 < splits ? ml[2 * (lane + 32)] : -INFINITY;
+    const float M = warp_max(fmaxf(m0, m1));
+    const float w0 = m0 == -INFINITY ? 0.f : expf(m0 - M), w1 = m1 == -INFINITY ? 0.f : expf(m1 - M);
+    if (lane < splits) weight[lane] = w0;
+    if (lane + 32 < splits) weight[lane + 32] = w1;
+    const float l = warp_sum((lane < splits ? w0 * ml[2 * lane + 1] : 0.f) +
+                             (lane + 32 < splits ? w1 * ml[2 * (lane + 32) + 1] : 0.f));
+    if (lane == 0) inv_l = l > 0.f ? 1.f / l : 0.f;
+  }
+  __syncthreads();
+  const float* po = part_o + row * splits * dv;
+  for (int c = threadIdx.x; c < dv; c += 128) {
     float acc = 0.f;
-    for (int s = 0; s < splits; ++s) {
-      const float m = ml[2 * s];
-      if (m != -INFINITY) acc = fmaf(expf(m - M), part_o[((size_t)row * splits + s) * dv + c], acc);
-    }
-    out[(size_t)row * dv + c] = __float2bfloat16_rn(acc * inv);
+#pragma unroll 4
+    for (int s = 0; s < splits; ++s) acc = fmaf(weight[s], po[(size_t)s * dv + c], acc);
+    out[row * dv + c] = __float2bfloat16_rn(acc * inv_l);
   }
 }
 
@@ -341,7 +350,7 @@ int tl_latent_attention_mma(const void* q, const void* pages, const int* block_t
                             int tiles, void* out, int tokens, int heads, int dk, int dv, int page_size, float scale,
                             int num_pages, int splits, float* part_o, float* part_ml, cudaStream_t stream) {
   if (tiles <= 0) return 0;
-  if (!tl_latent_attention_mma_supported(dk, dv) || splits < 1 || splits > 65535) return TL_ERR_UNSUPPORTED;
+  if (!tl_latent_attention_mma_supported(dk, dv) || splits < 1 || splits > MAX_SPLITS) return TL_ERR_UNSUPPORTED;
   if (splits > 1 && (!part_o || !part_ml || tile_req)) return TL_ERR_UNSUPPORTED;
   Args a;
   a.q = (const __nv_bfloat16*)q;
@@ -378,8 +387,8 @@ int tl_latent_attention_mma(const void* q, const void* pages, const int* block_t
   int code = TL_LAUNCH_CHECK();
   if (code || splits == 1) return code;
   const long long rows = (long long)tokens * heads;
-  tl::launch_kernel(latent_merge_kernel, (unsigned)((rows + 3) / 4), 128, 0, stream, (const float*)part_o,
-                    (const float*)part_ml, (__nv_bfloat16*)out, rows, splits, dv);
+  tl::launch_kernel(latent_merge_kernel, (unsigned)rows, 128, 0, stream, (const float*)part_o,
+                    (const float*)part_ml, (__nv_bfloat16*)out, splits, dv);
   return TL_LAUNCH_CHECK();
 }
 

@@ -349,12 +349,13 @@ def clamped_glu(gate_up: torch.Tensor, out: torch.Tensor, limit: float, alpha: f
 # ------------------------------------------------------------ delta-rule mixer
 def delta_prepare(proj, w2, w0, a_bias, gates, heads: int, dim: int, rank: int) -> None:
     """From the float32 projections ``proj`` [T, 5 H D + rank] (r | k | v | g | a' | l) to
-    ``gates`` [T, H, 3, D]: decay w, unit key u and a * u of every key channel (csrc/delta_rule.cu)."""
+    ``gates`` [T, H, 3, D]: decay w, unit key u and a * u of every key channel (csrc/delta_rule.cu).
+    ``w2`` is the decay's second matrix TRANSPOSED, [rank, H D]."""
     _need_cuda(proj, w2, w0, a_bias, gates)
     tokens = proj.shape[0]
     assert proj.dtype == torch.float32 and proj.stride(1) == 1 and proj.shape[1] == 5 * heads * dim + rank
     assert w2.dtype == w0.dtype == a_bias.dtype == gates.dtype == torch.float32
-    assert w2.is_contiguous() and w2.shape == (heads * dim, rank) and gates.is_contiguous()
+    assert w2.is_contiguous() and w2.shape == (rank, heads * dim) and gates.is_contiguous()
     assert gates.numel() == tokens * heads * 3 * dim
     code = _fn("delta_rule", "tl_delta_prepare")(proj.data_ptr(), proj.stride(0), w2.data_ptr(), w0.data_ptr(),
                                                  a_bias.data_ptr(), gates.data_ptr(), tokens, heads, dim, rank,

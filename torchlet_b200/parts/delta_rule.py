@@ -62,7 +62,8 @@ class GeneralDeltaMixer(Mixer):
         self.in_proj = Linear(fused, None, device, dtype)
         self.o_proj = Linear(tensors[prefix + "o"], None, device, dtype)
         f32 = lambda name: tensors[prefix + name].to(device=device, dtype=torch.float32).contiguous()
-        self.w2, self.w0, self.a_bias, self.norm_weight = f32("w2"), f32("w0"), f32("a.b"), f32("norm")
+        self.w0, self.a_bias, self.norm_weight = f32("w0"), f32("a.b"), f32("norm")
+        self.w2 = f32("w2").t().contiguous()  # [rank, H D]: the threads of a block read consecutive entries
 
     def forward(self, ctx, x, acc, cache) -> None:
         tokens, H, D = x.shape[0], self.num_heads, self.head_dim

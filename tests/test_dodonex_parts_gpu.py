@@ -305,3 +305,22 @@ def test_tensor_core_latent_attention_equals_the_plain_kernel(H, rank, rot):
                                  rank, page_size, 0.2, splits)
         assert torch.isfinite(got1.float()).all(), splits
         assert (got1.float() - want1.float()).abs().max() <= 2e-2 * want1.float().abs().max(), splits
+
+
+@pytest.mark.parametrize("tokens", [1, 8, 70, 300])
+def test_clamped_glu_in_the_epilogue_of_the_product(tokens):
+    """gate and up as one tensor-core product whose epilogue clamps and gates, against the plain
+    formula on the same bfloat16 operands; many values lie beyond the limit on either side."""
+    from torchlet_b200 import ops
+    from torchlet_b200.parts import swiglu_bf16
+
+    hidden, inter, limit = 64, 48, 0.9
+    x = rand(tokens, hidden, seed=90).bfloat16()
+    gate, up = rand(inter, hidden, seed=91, scale=0.3).bfloat16(), rand(inter, hidden, seed=92, scale=0.3).bfloat16()
+    g = torch.clamp(x.double() @ gate.double().T, max=limit)
+    u = torch.clamp(x.double() @ up.double().T, min=-limit, max=limit)
+    want = g * torch.sigmoid(1.702 * g) * (u + 1.0)
+    assert (x.double() @ gate.double().T > limit).any() and (x.double() @ up.double().T < -limit).any()
+    out = torch.empty(tokens, inter, device=DEV, dtype=torch.bfloat16)
+    ops.gemm_tc_glu(x.to(DEV), swiglu_bf16.interleave(gate.to(DEV), up.to(DEV)), out, limit, 1.702)
+    assert (out.cpu().double() - want).abs().max() <= 1e-2 * want.abs().max()

@@ -57,9 +57,20 @@ struct Params {
   int ahead;       // stages of weight tiles requested before the wait on the preceding kernel
   // persistent kernel (normal orientation): tile width, stages, tile counts
   int block_q, stages, row_tiles, num_tiles;
+  // the gated epilogue: limit 0: silu(gate) * up; limit > 0: g = min(gate, limit), u = clamp(up, +-limit),
+  // g * sigmoid(alpha g) * (u + 1)
+  float glu_limit, glu_alpha;
 };
 
 __device__ __forceinline__ float silu(float g) { return g / (1.f + __expf(-g)); }
+__device__ __forceinline__ float gated(float g, float u, float limit, float alpha) {
+  if (limit > 0.f) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.f + __expf(-alpha * g)) * (u + 1.f);
+  }
+  return silu(g) * u;
+}
 
 // 32 accumulator values of output row m, columns n0 .. n0+31 (normal orientation).
 __device__ __forceinline__ void epilogue_chunk(const Params& p, int m, int n0, const float (&v)[32], int cols = 32) {
@@ -71,8 +82,8 @@ __device__ __forceinline__ void epilogue_chunk(const Params& p, int m, int n0, c
     uint32_t packed[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const float a = silu(v[2 * j]) * v[2 * j + 16];
-      const float b = silu(v[2 * j + 1]) * v[2 * j + 17];
+      const float a = gated(v[2 * j], v[2 * j + 16], p.glu_limit, p.glu_alpha);
+      const float b = gated(v[2 * j + 1], v[2 * j + 17], p.glu_limit, p.glu_alpha);
       __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
       packed[j] = *reinterpret_cast<uint32_t*>(&h);
     }
@@ -338,7 +349,7 @@ gemm_tc_swapped_kernel(const __grid_constant__ CUtensorMap map_row, const __grid
           const float up = __shfl_down_sync(0xffffffffu, v[j], 16);
           const int m = col0 + c + j;
           if (live && lane < 16 && m < p.cols)
-            ((__nv_bfloat16*)p.out)[(size_t)m * p.ldo + out_col] = __float2bfloat16_rn(silu(v[j]) * up);
+            ((__nv_bfloat16*)p.out)[(size_t)m * p.ldo + out_col] = __float2bfloat16_rn(gated(v[j], up, p.glu_limit, p.glu_alpha));
         }
       } else if (live) {
         const float b = p.bias ? p.bias[row] : 0.f;
@@ -680,7 +691,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_co
 
 // Adds the split partials [splits][M][N] in ascending split order and applies the epilogue.
 __global__ void splitk_finish_kernel(const float* __restrict__ partial, int splits, int M, int N,
-                                     const float* __restrict__ bias, int epilogue, void* out, long long ldo) {
+                                     const float* __restrict__ bias, int epilogue, void* out, long long ldo,
+                                     float glu_limit, float glu_alpha) {
   tl::pdl_wait();               // everything before us in the stream is complete and visible
   tl::pdl_launch_dependents();  // the next kernel may start its own prologue
 
@@ -696,7 +708,7 @@ __global__ void splitk_finish_kernel(const float* __restrict__ partial, int spli
       gate += partial[s * plane + (size_t)m * N + g];
       up += partial[s * plane + (size_t)m * N + g + 16];
     }
-    ((__nv_bfloat16*)out)[(size_t)m * ldo + c] = __float2bfloat16_rn(silu(gate) * up);
+    ((__nv_bfloat16*)out)[(size_t)m * ldo + c] = __float2bfloat16_rn(gated(gate, up, glu_limit, glu_alpha));
     return;
   }
   float v = 0.f;
@@ -960,9 +972,30 @@ int tl_gemm_tc_error() {
 // between rows (multiples of 8, bases 16-byte aligned).  epilogue: 0 bf16 out + bias,
 // 1 float32 out += result, 2 SwiGLU over 16-interleaved gate/up rows of w -> bf16
 // [M, N/2], 3 float32 out.  workspace: float32 scratch of at least tl_gemm_tc_plan bytes.
+static int gemm_tc_impl(const void* x, const void* w, const float* bias, void* out, long long ldo, int epilogue, int M,
+                        int N, int K, long long ldx, long long ldw, void* workspace, long long workspace_bytes,
+                        int defer, int* splits_out, float glu_limit, float glu_alpha, cudaStream_t stream);
+
 int tl_gemm_tc(const void* x, const void* w, const float* bias, void* out, long long ldo, int epilogue, int M,
                int N, int K, long long ldx, long long ldw, void* workspace, long long workspace_bytes, int defer,
                int* splits_out, cudaStream_t stream) {
+  return gemm_tc_impl(x, w, bias, out, ldo, epilogue, M, N, K, ldx, ldw, workspace, workspace_bytes, defer, splits_out,
+                      0.f, 0.f, stream);
+}
+
+// The gated epilogue (2) with a clamp: g = min(gate, limit), u = clamp(up, -limit, limit),
+// out = g * sigmoid(alpha g) * (u + 1);  limit > 0.
+int tl_gemm_tc_glu(const void* x, const void* w, void* out, long long ldo, int M, int N, int K, long long ldx,
+                   long long ldw, void* workspace, long long workspace_bytes, float limit, float alpha,
+                   cudaStream_t stream) {
+  if (!(limit > 0.f)) return TL_ERR_UNSUPPORTED;
+  return gemm_tc_impl(x, w, nullptr, out, ldo, EPI_SWIGLU_BF16, M, N, K, ldx, ldw, workspace, workspace_bytes, 0,
+                      nullptr, limit, alpha, stream);
+}
+
+static int gemm_tc_impl(const void* x, const void* w, const float* bias, void* out, long long ldo, int epilogue, int M,
+                        int N, int K, long long ldx, long long ldw, void* workspace, long long workspace_bytes,
+                        int defer, int* splits_out, float glu_limit, float glu_alpha, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || epilogue < 0 || epilogue > 3) return TL_ERR_UNSUPPORTED;
   if (epilogue == EPI_SWIGLU_BF16 && (N % 32 || bias)) return TL_ERR_UNSUPPORTED;
@@ -977,6 +1010,8 @@ int tl_gemm_tc(const void* x, const void* w, const float* bias, void* out, long 
   p.partial = nullptr;
   p.splits = 1;
   p.ahead = 8;  // all stages
+  p.glu_limit = glu_limit;
+  p.glu_alpha = glu_alpha;
   if (splits_out) *splits_out = 0;
   CUtensorMap map_row, map_col;
   int rc;
@@ -1013,7 +1048,7 @@ int tl_gemm_tc(const void* x, const void* w, const float* bias, void* out, long 
     const int out_cols = epilogue == EPI_SWIGLU_BF16 ? N / 2 : N;
     const long long total = (long long)M * out_cols;
     tl::launch_kernel(splitk_finish_kernel, (unsigned)((total + 255) / 256), 256, 0, stream, p.partial, plan.splits, M, N, bias,
-                                                                             epilogue, out, ldo);
+                                                                             epilogue, out, ldo, glu_limit, glu_alpha);
     return TL_LAUNCH_CHECK();
   }
   p.rows = M;
@@ -1063,7 +1098,7 @@ int tl_gemm_tc(const void* x, const void* w, const float* bias, void* out, long 
     const int out_cols = epilogue == EPI_SWIGLU_BF16 ? N / 2 : N;
     const long long total = (long long)M * out_cols;
     tl::launch_kernel(splitk_finish_kernel, (unsigned)((total + 255) / 256), 256, 0, stream, p.partial, plan.splits, M, N,
-                      bias, epilogue, out, ldo);
+                      bias, epilogue, out, ldo, glu_limit, glu_alpha);
     return TL_LAUNCH_CHECK();
   }
   p.k_blocks_per_split = p.k_blocks;

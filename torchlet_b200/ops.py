@@ -52,6 +52,8 @@ _SIGNATURES = {
     "gemm_tc": {
         "tl_gemm_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_longlong,
                        c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p],
+        "tl_gemm_tc_glu": [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_longlong, c_longlong, c_void_p,
+                           c_longlong, c_float, c_float, c_void_p],
         "tl_gemm_tc_plan": [c_int, c_int, c_int, c_void_p, c_void_p],
         "tl_gemm_tc_error": [],
         "tl_gemm_tc_wait_selftest": [c_int, c_void_p],
@@ -576,6 +578,23 @@ def gemm_tc(x, w, out, bias=None, epilogue=EPI_STORE_BF16, cta_pairs=None) -> No
         w.stride(0), _ptr(ws), ws.numel() * 4 if ws is not None else 0, {None: 0, True: 2, False: 3}[cta_pairs], None,
         _stream())
     _check(code, "gemm_tc", kernels)
+
+
+def gemm_tc_glu(x, w, out, limit: float, alpha: float) -> None:
+    """out = g * sigmoid(alpha g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit), where gate
+    and up are the 16-interleaved rows of ``w`` applied to ``x``: the product and the activation as one kernel
+    (the gated epilogue of csrc/gemm_tc.cu).  out bfloat16 [M, N / 2]."""
+    _need_cuda(x, w, out)
+    _release_workspace()
+    M, K = x.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and out.stride(1) == 1 and out.dtype == torch.bfloat16 and out.shape == (M, N // 2)
+    need, _, splits = _gemm_plan(M, N, K)
+    ws = _workspace(x.device, need) if need else None
+    code = _fn("gemm_tc", "tl_gemm_tc_glu")(
+        x.data_ptr(), w.data_ptr(), out.data_ptr(), out.stride(0), M, N, K, x.stride(0), w.stride(0), _ptr(ws),
+        ws.numel() * 4 if ws is not None else 0, float(limit), float(alpha), _stream())
+    _check(code, "gemm_tc_glu", 2 if need and splits > 1 else 1)
 
 
 def gemm_tc_deferred(x, w):

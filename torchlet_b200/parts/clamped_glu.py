@@ -24,6 +24,7 @@ class ClampedGLU(FeedForward):
         self.limit = float(p["limit"])
         self.alpha = float(p.get("alpha", 1.702))
         self.gate_up_proj: Linear | None = None
+        self.gate_up_interleaved = None  # bfloat16 fused path: gate/up rows interleaved by 16
         self.down_proj: Linear | None = None
 
     @classmethod
@@ -39,12 +40,25 @@ class ClampedGLU(FeedForward):
         return [TensorSpec(gate, (inter, hidden)), TensorSpec(up, (inter, hidden)), TensorSpec(down, (hidden, inter))]
 
     def load(self, tensors: dict, prefix: str, device, dtype) -> None:
+        from . import swiglu_bf16
+
         gate, up, down = self._names(self.spec, prefix)
-        self.gate_up_proj = Linear(torch.cat([tensors[gate], tensors[up]], dim=0), None, device, dtype)
+        if dtype == torch.bfloat16 and swiglu_bf16.usable(self.hidden_size, self.intermediate_size):
+            # bfloat16: ONE tcgen05 product over the 16-interleaved gate and up rows, the activation in its epilogue
+            self.gate_up_interleaved = swiglu_bf16.interleave(
+                tensors[gate].to(device=device, dtype=dtype), tensors[up].to(device=device, dtype=dtype))
+        else:
+            self.gate_up_proj = Linear(torch.cat([tensors[gate], tensors[up]], dim=0), None, device, dtype)
         self.down_proj = Linear(tensors[down], None, device, dtype)
 
     def forward(self, ctx, x, acc) -> None:
         tokens = x.shape[0]
+        if self.gate_up_interleaved is not None and ops.gemm_tc_supported(x, self.gate_up_interleaved):
+            act = ctx.buffer("clamped_glu.act", (tokens, self.intermediate_size), ctx.dtype)
+            ops.gemm_tc_glu(x, self.gate_up_interleaved, act, self.limit, self.alpha)
+            if not self.down_proj.accumulate_later(ctx, act, acc):
+                self.down_proj.forward(act, acc, accumulate=True)
+            return
         gate_up = ctx.buffer("clamped_glu.gate_up", (tokens, 2 * self.intermediate_size), ctx.dtype)
         self.gate_up_proj.forward(x, gate_up)
         act = ctx.buffer("clamped_glu.act", (tokens, self.intermediate_size), ctx.dtype)

@@ -50,6 +50,13 @@ CASES = {
               layer("general_delta", {"heads": 1, "dim": 20, "decay_rank": 3}),
               layer("latent_attention", latent(5, 12, 2, 4, 18, 20, base=300.0, scale=0.4), ff=36, limit=3.0),
           ]},
+    # nothing is a multiple of 4: every kernel's plain form (odd rows in the cache, an odd width)
+    "S": {"architecture": "Dodonex", "vocab": 33, "width": 50, "embedding": {"scale": 2.0},
+          "norm": {"eps": 1e-5, "groups": 5}, "residual_mult": 0.9, "logit_scale": 3.0, "token_side": {"dim": 3},
+          "layers": [
+              layer("general_delta", {"heads": 2, "dim": 10, "decay_rank": 3}, ff=21, limit=1.0),
+              layer("latent_attention", latent(2, 5, 6, 3, 13, 7, base=50.0), ff=21, limit=1.0),
+          ]},
     # sizes the tensor-core kernels take: multiples of 16 throughout, 64-wide delta heads
     "R": {"architecture": "Dodonex", "vocab": 211, "width": 128, "embedding": {"scale": 3.0},
           "norm": {"eps": 1e-5, "groups": 2}, "residual_mult": 0.8, "logit_scale": 0.5, "token_side": {"dim": 16},

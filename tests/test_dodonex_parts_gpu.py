@@ -99,7 +99,7 @@ def delta_weights(W, H, D, rank, seed):
     return out
 
 
-@pytest.mark.parametrize("H,D,rank", [(2, 24, 5), (1, 64, 16), (3, 40, 7), (2, 100, 4), (1, 16, 2)])
+@pytest.mark.parametrize("H,D,rank", [(2, 24, 5), (1, 64, 16), (3, 40, 7), (2, 100, 4), (1, 16, 2), (1, 200, 3), (1, 256, 8)])
 def test_delta_rule_kernels_carry_the_state(H, D, rank):
     """prepare, scan and finish against the plain recurrence: a sequence in three portions (the
     state must carry), beside another request; then the first slot is used again from zero."""

@@ -57,7 +57,7 @@ delta_prepare_kernel(const float* __restrict__ proj, int proj_stride, const floa
 #pragma unroll
   for (int tt = 0; tt < PREP_TOKENS; ++tt) inner[tt] = w0[c];
   if (on) {
-#pragma unroll 4
+#pragma unroll 8
     for (int j = 0; j < rank; ++j) {
       const float w = w2t[(size_t)j * hd + c];
 #pragma unroll

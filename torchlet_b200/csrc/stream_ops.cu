@@ -25,6 +25,25 @@ __global__ void fill_zero_kernel(float4* __restrict__ p, size_t quads) {
   if (i < quads) p[i] = make_float4(0.f, 0.f, 0.f, 0.f);
 }
 
+// The same one element a thread, for sizes or addresses the 16-byte forms do not take.
+__global__ void fill_zero_scalar_kernel(float* __restrict__ p, size_t n) {
+  tl::pdl_launch_dependents();
+  tl::pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) p[i] = 0.f;
+}
+
+__global__ void scaled_add_scalar_kernel(float* __restrict__ acc, const float* __restrict__ delta, float m,
+                                         __nv_bfloat16* __restrict__ cast, size_t n) {
+  tl::pdl_launch_dependents();
+  tl::pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float a = fmaf(m, delta[i], acc[i]);
+  acc[i] = a;
+  if (cast) cast[i] = __float2bfloat16_rn(a);
+}
+
 __global__ void scale_kernel(float* __restrict__ p, float alpha, size_t n) {
   tl::pdl_launch_dependents();
   tl::pdl_wait();
@@ -116,7 +135,10 @@ extern "C" {
 
 int tl_fill_zero(float* p, long long n, cudaStream_t stream) {
   if (n <= 0) return 0;
-  if (n % 4 || (reinterpret_cast<uintptr_t>(p) & 15)) return TL_ERR_UNSUPPORTED;
+  if (n % 4 || (reinterpret_cast<uintptr_t>(p) & 15)) {
+    tl::launch_kernel(fill_zero_scalar_kernel, (unsigned)(((size_t)n + 255) / 256), 256, 0, stream, p, (size_t)n);
+    return TL_LAUNCH_CHECK();
+  }
   const size_t quads = (size_t)n / 4;
   tl::launch_kernel(fill_zero_kernel, (unsigned)((quads + 255) / 256), 256, 0, stream, (float4*)p, quads);
   return TL_LAUNCH_CHECK();
@@ -131,8 +153,11 @@ int tl_scale(float* p, float alpha, long long n, cudaStream_t stream) {
 int tl_scaled_add(float* acc, const float* delta, float m, void* cast, long long n, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (n % 4 || ((reinterpret_cast<uintptr_t>(acc) | reinterpret_cast<uintptr_t>(delta)) & 15) ||
-      (reinterpret_cast<uintptr_t>(cast) & 7))
-    return TL_ERR_UNSUPPORTED;
+      (reinterpret_cast<uintptr_t>(cast) & 7)) {
+    tl::launch_kernel(scaled_add_scalar_kernel, (unsigned)(((size_t)n + 255) / 256), 256, 0, stream, acc, delta, m,
+                      (__nv_bfloat16*)cast, (size_t)n);
+    return TL_LAUNCH_CHECK();
+  }
   const size_t quads = (size_t)n / 4;
   tl::launch_kernel(scaled_add_kernel, (unsigned)((quads + 255) / 256), 256, 0, stream, (float4*)acc,
                     (const float4*)delta, m, (uint2*)cast, quads);

@@ -289,7 +289,7 @@ def sample(logits, out, temperature=None, seed=None, counter=None) -> None:
 
 # ------------------------------------------------- around the residual stream
 def fill_zero(x: torch.Tensor) -> None:
-    """x = 0;  float32, contiguous, a multiple of 4 elements."""
+    """x = 0;  float32, contiguous."""
     _need_cuda(x)
     assert x.dtype == torch.float32 and x.is_contiguous()
     _check(_fn("stream_ops", "tl_fill_zero")(x.data_ptr(), x.numel(), _stream()), "fill_zero")

@@ -87,8 +87,9 @@ class LatentAttentionMixer(Mixer):
         self.own_kv = bool(p.get("own_kv", True))
         if self.rot_dims % 2 or self.rot_dims > self.rot_dim:
             raise ValueError("rot_dims must be even and at most rot_dim")
-        if self.kv_rank > 512:
-            raise ValueError(f"kv_rank {self.kv_rank} is not supported by the latent attention kernels (up to 512)")
+        if self.kv_rank > 1024 or self.head_dim > 1024:
+            raise ValueError(f"kv_rank {self.kv_rank} / head_dim {self.head_dim} are not supported by the latent "
+                             "attention kernels (up to 1024)")
         self.row = self.kv_rank + self.rot_dim  # a token's cache row
         self.down_proj: Linear | None = None
         self.uq_proj: Linear | None = None

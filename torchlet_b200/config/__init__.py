@@ -10,12 +10,14 @@ from .registry import (
 from .spec import LayerSpec, ModelSpec, NormSlot, PartSpec, ScheduleEntry
 from .qwen2 import Qwen2Config
 from .dodonex import DodonexConfig
+from .numuzen import NumuzenConfig
 
 __all__ = [
     "DodonexConfig",
     "EngineConfig",
     "LayerSpec",
     "ModelSpec",
+    "NumuzenConfig",
     "NormSlot",
     "PartSpec",
     "Qwen2Config",

@@ -6,6 +6,10 @@
 // into steps, on the batch, or on the pages used.  Scores, softmax and the weighted
 // sum are float32; T is the storage type of queries, pages and output.
 //
+// Options: ``softcap`` > 0 bounds a score, s <- softcap tanh(s / softcap); ``sink`` adds one to the
+// softmax's denominator (a key of score 0 that has no value); ``gate`` (float32 rows) multiplies the
+// output element by element with sigmoid(gate).
+//
 // This is the true 32-bit kernel and the any-size bfloat16 kernel (head_dim any
 // multiple of 8 up to 256, any head counts, any page size).
 //
@@ -30,7 +34,8 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restr
                          const int* __restrict__ block_table, int table_width,
                          const int* __restrict__ token_req, const int* __restrict__ positions,
                          T* __restrict__ out, int out_stride, int tokens, int nh, int nkv, int d,
-                         int page_size, int window, float scale, int num_pages) {
+                         int page_size, int window, float scale, int num_pages, float softcap, int sink,
+                         const float* __restrict__ gate, int gate_stride) {
   tl::pdl_wait();               // everything before us in the stream is complete and visible
   tl::pdl_launch_dependents();  // the next kernel may start its own prologue
 
@@ -52,7 +57,9 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restr
   const size_t k_off = (size_t)kvh * page_size * d;
   const size_t v_off = ((size_t)nkv + kvh) * page_size * d;
 
-  float m = -INFINITY, l = 0.f;
+  // the sink is a key of score 0 and no value that every query sees: the running maximum starts
+  // at 0 with a weight of exp(0) in the denominator
+  float m = sink ? 0.f : -INFINITY, l = sink ? 1.f : 0.f;
   float acc[MAX_D / 32];
 #pragma unroll
   for (int c = 0; c < MAX_D / 32; ++c) acc[c] = 0.f;
@@ -76,6 +83,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restr
         for (int j = 0; j < 8; ++j) dot = fmaf(qs[warp][i + j], kv[j], dot);
       }
       s = dot * scale;
+      if (softcap > 0.f) s = softcap * tanhf(s / softcap);
     }
     const float new_m = fmaxf(m, warp_max(s));
     const float corr = expf(m - new_m);  // first tile: exp(-inf) = 0
@@ -102,7 +110,11 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restr
 #pragma unroll
   for (int c = 0; c < MAX_D / 32; ++c) {
     const int i = lane + 32 * c;
-    if (i < d) orow[i] = from_float<T>(acc[c] * inv);
+    if (i < d) {
+      float v = acc[c] * inv;
+      if (gate) v *= 1.f / (1.f + expf(-gate[(size_t)t * gate_stride + (size_t)h * d + i]));
+      orow[i] = from_float<T>(v);
+    }
   }
 }
 
@@ -114,7 +126,8 @@ extern "C" int tl_attention_generic(const void* q, int q_stride, const void* pag
                                     const int* block_table, int table_width, const int* token_req,
                                     const int* positions, void* out, int out_stride, int tokens,
                                     int nh, int nkv, int d, int page_size, int window, float scale,
-                                    int num_pages, cudaStream_t stream) {
+                                    int num_pages, float softcap, int sink, const float* gate, int gate_stride,
+                                    cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (d <= 0 || d > MAX_D || d % 8 || nkv <= 0 || nh % nkv || page_size <= 0 || q_stride % 8)
     return TL_ERR_UNSUPPORTED;
@@ -123,11 +136,12 @@ extern "C" int tl_attention_generic(const void* q, int q_stride, const void* pag
   if (dtype == TL_DTYPE_F32)
     tl::launch_kernel(attention_generic_kernel<float>, blocks, WARPS * 32, 0, stream, 
         (const float*)q, q_stride, (const float*)pages, block_table, table_width, token_req,
-        positions, (float*)out, out_stride, tokens, nh, nkv, d, page_size, window, scale, num_pages);
+        positions, (float*)out, out_stride, tokens, nh, nkv, d, page_size, window, scale, num_pages, softcap, sink,
+        gate, gate_stride);
   else
     tl::launch_kernel(attention_generic_kernel<__nv_bfloat16>, blocks, WARPS * 32, 0, stream, 
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)pages, block_table, table_width,
         token_req, positions, (__nv_bfloat16*)out, out_stride, tokens, nh, nkv, d, page_size, window,
-        scale, num_pages);
+        scale, num_pages, softcap, sink, gate, gate_stride);
   return TL_LAUNCH_CHECK();
 }

@@ -1,0 +1,311 @@
+// A routed feed-forward (mixture of experts): every token goes through ``top`` of ``experts`` small
+// gated feed-forwards.  Everything is planned on the device, so a step needs no answer from the GPU
+// and a step of single tokens can be captured in a CUDA graph.
+//
+//   route     one warp per token: router logits z = W_r x in float32 (ascending k), scores
+//             sigmoid(z) or softmax(z), the ``top`` largest (the lower index wins a tie), optionally
+//             renormalized to sum 1;
+//   plan      one block: rows per expert, each expert's rows rounded up to whole row tiles of
+//             ``tile`` rows so that a tile of the grouped products belongs to ONE expert; the
+//             position of every (token, choice) in that expert-sorted order; the expert of every tile;
+//   scatter   the expert-sorted input rows: x[token] (times the choice's weight where the weight
+//             multiplies the expert's INPUT);
+//   products  out[row] = W_e(row) . in[row] over the sorted rows, CUDA cores, ascending k: with the
+//             gated activation g sigmoid(alpha g) (u + 1), g = min(gate, limit), u = clamp(up, +-limit),
+//             over [gate; up] stacked weights, or plain (the down projection, float32 output);
+//   combine   side[token] += sum over the token's choices, in the order of the choices, of the down
+//             rows (times the weight where it multiplies the OUTPUT).
+//
+// A row's result depends on the row alone (its expert, its input), never on where it stands in the
+// sorted order or on which other tokens are in the step.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace {
+
+using namespace tl;
+
+constexpr int ROUTE_WARPS = 4;
+constexpr int MAX_EXPERTS = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+moe_route_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ router, int* __restrict__ choice,
+                 float* __restrict__ weight, int tokens, int hidden, int experts, int top, int softmax_scores,
+                 int renormalize) {
+  tl::pdl_launch_dependents();
+  tl::pdl_wait();
+  __shared__ float score[ROUTE_WARPS][MAX_EXPERTS];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * ROUTE_WARPS + warp;
+  if (t >= tokens) return;
+  const T* row = x + (size_t)t * ldx;
+  for (int e = 0; e < experts; ++e) {
+    const float* w = router + (size_t)e * hidden;
+    float part = 0.f;
+    for (int k = lane; k < hidden; k += 32) part = fmaf(to_float(row[k]), w[k], part);
+    part = warp_sum(part);
+    if (lane == 0) score[warp][e] = part;
+  }
+  __syncwarp();
+  if (softmax_scores) {
+    float m = -INFINITY;
+    for (int e = lane; e < experts; e += 32) m = fmaxf(m, score[warp][e]);
+    m = warp_max(m);
+    float l = 0.f;
+    for (int e = lane; e < experts; e += 32) l += expf(score[warp][e] - m);
+    l = warp_sum(l);
+    for (int e = lane; e < experts; e += 32) score[warp][e] = expf(score[warp][e] - m) / l;
+  } else {
+    for (int e = lane; e < experts; e += 32) score[warp][e] = 1.f / (1.f + expf(-score[warp][e]));
+  }
+  __syncwarp();
+  float total = 0.f;
+  for (int j = 0; j < top; ++j) {
+    float best = -INFINITY;
+    int at = experts;
+    for (int e = lane; e < experts; e += 32) {
+      const float s = score[warp][e];
+      if (s > best) { best = s; at = e; }  // ascending e: the lower index keeps a tie
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float other = __shfl_xor_sync(0xffffffffu, best, o);
+      const int other_at = __shfl_xor_sync(0xffffffffu, at, o);
+      if (other > best || (other == best && other_at < at)) { best = other; at = other_at; }
+    }
+    if (at >= experts) at = 0;  // every score was NaN: still a valid expert
+    total += best;
+    if (lane == 0) {
+      choice[(size_t)t * top + j] = at;
+      weight[(size_t)t * top + j] = best;
+      score[warp][at] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  if (renormalize && lane < top) weight[(size_t)t * top + lane] /= total;
+  if (renormalize)
+    for (int j = 32 + lane; j < top; j += 32) weight[(size_t)t * top + j] /= total;
+}
+
+// plan[0] = tiles in use; plan[1 ..] = expert of every tile (-1: none).
+constexpr int PLAN_NT = 1024;
+
+__global__ void __launch_bounds__(PLAN_NT)
+moe_plan_kernel(const int* __restrict__ choice, int* __restrict__ position, int* __restrict__ plan, int entries,
+                int experts, int tile, int max_tiles) {
+  tl::pdl_launch_dependents();
+  tl::pdl_wait();
+  __shared__ int count[MAX_EXPERTS], start[MAX_EXPERTS], cursor[MAX_EXPERTS];
+  for (int e = threadIdx.x; e < experts; e += PLAN_NT) count[e] = cursor[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < entries; i += PLAN_NT) atomicAdd(&count[choice[i]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int tiles = 0;
+    for (int e = 0; e < experts; ++e) {
+      start[e] = tiles * tile;
+      const int mine = (count[e] + tile - 1) / tile;
+      for (int j = 0; j < mine && tiles + j < max_tiles; ++j) plan[1 + tiles + j] = e;
+      tiles += mine;
+    }
+    plan[0] = tiles < max_tiles ? tiles : max_tiles;
+    for (int j = tiles; j < max_tiles; ++j) plan[1 + j] = -1;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < entries; i += PLAN_NT) {
+    const int e = choice[i];
+    position[i] = start[e] + atomicAdd(&cursor[e], 1);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_scatter_kernel(const T* __restrict__ x, int ldx, const int* __restrict__ position, const float* __restrict__ weight,
+                   T* __restrict__ sorted, int hidden, int top, int weighted) {
+  tl::pdl_launch_dependents();
+  tl::pdl_wait();
+  const int entry = blockIdx.x;
+  const int t = entry / top;
+  const float w = weighted ? weight[entry] : 1.f;
+  const T* from = x + (size_t)t * ldx;
+  T* to = sorted + (size_t)position[entry] * hidden;
+  for (int k = threadIdx.x; k < hidden; k += 128) to[k] = weighted ? from_float<T>(w * to_float(from[k])) : from[k];
+}
+
+constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
+
+// out[row, n] over the rows of tile blockIdx.y, whose expert the plan names.  GLU: w holds, per
+// expert, [gate (N rows); up (N rows)] and out = act(gate . x, up . x); else out = w_e . x.
+template <typename T, typename OutT, bool GLU>
+__global__ void __launch_bounds__(256)
+moe_gemm_simt_kernel(const T* __restrict__ x, const T* __restrict__ w, OutT* __restrict__ out,
+                     const int* __restrict__ plan, int N, int K, float limit, float alpha) {
+  tl::pdl_wait();
+  tl::pdl_launch_dependents();
+  if ((int)blockIdx.y >= plan[0]) return;
+  const int expert = plan[1 + blockIdx.y];
+  if (expert < 0) return;
+  __shared__ float xs[BK][BM + 1];
+  __shared__ float ws[BK][BN + 1];
+  __shared__ float us[GLU ? BK : 1][BN + 1];
+  const int tid = threadIdx.x;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int tx = tid % 16, ty = tid / 16;
+  const T* we = w + (size_t)expert * (GLU ? 2 : 1) * N * K;
+  float acc[TM][TN], acc_up[GLU ? TM : 1][TN];
+#pragma unroll
+  for (int i = 0; i < TM; ++i)
+#pragma unroll
+    for (int j = 0; j < TN; ++j) {
+      acc[i][j] = 0.f;
+      if constexpr (GLU) acc_up[i][j] = 0.f;
+    }
+  for (int k0 = 0; k0 < K; k0 += BK) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int e = tid + i * 256;
+      const int r = e / BK, c = e % BK;
+      const int k = k0 + c;
+      float xv = 0.f, wv = 0.f, uv = 0.f;
+      if (k < K) {
+        xv = to_float(x[(size_t)(m0 + r) * K + k]);
+        if (n0 + r < N) {
+          wv = to_float(we[(size_t)(n0 + r) * K + k]);
+          if (GLU) uv = to_float(we[(size_t)(N + n0 + r) * K + k]);
+        }
+      }
+      xs[c][r] = xv;
+      ws[c][r] = wv;
+      if constexpr (GLU) us[c][r] = uv;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int c = 0; c < BK; ++c) {
+      float xa[TM], wb[TN], ub[TN];
+#pragma unroll
+      for (int i = 0; i < TM; ++i) xa[i] = xs[c][ty * TM + i];
+#pragma unroll
+      for (int j = 0; j < TN; ++j) {
+        wb[j] = ws[c][tx * TN + j];
+        if constexpr (GLU) ub[j] = us[c][tx * TN + j];
+      }
+#pragma unroll
+      for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+          acc[i][j] = fmaf(xa[i], wb[j], acc[i][j]);
+          if constexpr (GLU) acc_up[i][j] = fmaf(xa[i], ub[j], acc_up[i][j]);
+        }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < TM; ++i) {
+    const int m = m0 + ty * TM + i;
+#pragma unroll
+    for (int j = 0; j < TN; ++j) {
+      const int n = n0 + tx * TN + j;
+      if (n >= N) continue;
+      float v = acc[i][j];
+      if constexpr (GLU) {
+        const float g = fminf(v, limit);
+        const float u = fminf(fmaxf(acc_up[i][j], -limit), limit);
+        v = g / (1.f + expf(-alpha * g)) * (u + 1.f);
+      }
+      out[(size_t)m * N + n] = from_float<OutT>(v);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(128)
+moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ position, const float* __restrict__ weight,
+                   float* __restrict__ side, int hidden, int top, int weighted) {
+  tl::pdl_launch_dependents();
+  tl::pdl_wait();
+  const int t = blockIdx.x;
+  for (int c = threadIdx.x; c < hidden; c += 128) {
+    float sum = 0.f;
+    for (int j = 0; j < top; ++j) {
+      const float v = y[(size_t)position[(size_t)t * top + j] * hidden + c];
+      sum = weighted ? fmaf(weight[(size_t)t * top + j], v, sum) : sum + v;
+    }
+    side[(size_t)t * hidden + c] += sum;
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+int tl_moe_tile_rows() { return BM; }
+
+// choice int32 [tokens, top], weight float32 [tokens, top]; router float32 [experts, hidden].
+int tl_moe_route(const void* x, int ldx, int dtype, const float* router, int* choice, float* weight, int tokens,
+                 int hidden, int experts, int top, int softmax_scores, int renormalize, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (experts <= 0 || experts > MAX_EXPERTS || top <= 0 || top > experts) return TL_ERR_UNSUPPORTED;
+  const unsigned blocks = (tokens + ROUTE_WARPS - 1) / ROUTE_WARPS;
+  if (dtype == TL_DTYPE_F32)
+    tl::launch_kernel(moe_route_kernel<float>, blocks, ROUTE_WARPS * 32, 0, stream, (const float*)x, ldx, router, choice,
+                      weight, tokens, hidden, experts, top, softmax_scores, renormalize);
+  else
+    tl::launch_kernel(moe_route_kernel<__nv_bfloat16>, blocks, ROUTE_WARPS * 32, 0, stream, (const __nv_bfloat16*)x,
+                      ldx, router, choice, weight, tokens, hidden, experts, top, softmax_scores, renormalize);
+  return TL_LAUNCH_CHECK();
+}
+
+// position int32 [entries]; plan int32 [1 + max_tiles].
+int tl_moe_plan(const int* choice, int* position, int* plan, int entries, int experts, int tile, int max_tiles,
+                cudaStream_t stream) {
+  if (entries <= 0) return 0;
+  if (experts <= 0 || experts > MAX_EXPERTS || tile <= 0) return TL_ERR_UNSUPPORTED;
+  tl::launch_kernel(moe_plan_kernel, 1, PLAN_NT, 0, stream, choice, position, plan, entries, experts, tile, max_tiles);
+  return TL_LAUNCH_CHECK();
+}
+
+int tl_moe_scatter(const void* x, int ldx, int dtype, const int* position, const float* weight, void* sorted,
+                   int tokens, int hidden, int top, int weighted, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (dtype == TL_DTYPE_F32)
+    tl::launch_kernel(moe_scatter_kernel<float>, (unsigned)(tokens * top), 128, 0, stream, (const float*)x, ldx, position,
+                      weight, (float*)sorted, hidden, top, weighted);
+  else
+    tl::launch_kernel(moe_scatter_kernel<__nv_bfloat16>, (unsigned)(tokens * top), 128, 0, stream,
+                      (const __nv_bfloat16*)x, ldx, position, weight, (__nv_bfloat16*)sorted, hidden, top, weighted);
+  return TL_LAUNCH_CHECK();
+}
+
+// x [rows, K] sorted rows (rows = max_tiles * 64), w [experts, (2) N, K], out [rows, N].
+int tl_moe_gemm_simt(const void* x, const void* w, int dtype, void* out, int out_dtype, const int* plan, int max_tiles,
+                     int N, int K, int glu, float limit, float alpha, cudaStream_t stream) {
+  if (max_tiles <= 0 || N <= 0) return 0;
+  if (K <= 0 || max_tiles > 65535) return TL_ERR_UNSUPPORTED;
+  dim3 grid((N + BN - 1) / BN, max_tiles);
+#define TL_MOE(T, OutT, GLU)                                                                                        \
+  tl::launch_kernel(moe_gemm_simt_kernel<T, OutT, GLU>, grid, 256, 0, stream, (const T*)x, (const T*)w, (OutT*)out, \
+                    plan, N, K, limit, alpha)
+  if (dtype == TL_DTYPE_F32) {
+    if (out_dtype != TL_DTYPE_F32) return TL_ERR_UNSUPPORTED;
+    if (glu) TL_MOE(float, float, true); else TL_MOE(float, float, false);
+  } else if (glu) {
+    if (out_dtype != TL_DTYPE_BF16) return TL_ERR_UNSUPPORTED;
+    TL_MOE(__nv_bfloat16, __nv_bfloat16, true);
+  } else {
+    if (out_dtype != TL_DTYPE_F32) return TL_ERR_UNSUPPORTED;
+    TL_MOE(__nv_bfloat16, float, false);
+  }
+#undef TL_MOE
+  return TL_LAUNCH_CHECK();
+}
+
+int tl_moe_combine(const float* y, const int* position, const float* weight, float* side, int tokens, int hidden,
+                   int top, int weighted, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  tl::launch_kernel(moe_combine_kernel, (unsigned)tokens, 128, 0, stream, y, position, weight, side, hidden, top,
+                    weighted);
+  return TL_LAUNCH_CHECK();
+}
+
+}  // extern "C"

@@ -65,6 +65,7 @@ class StepContext:
         self._runner = runner
         self.dtype: torch.dtype = runner.dtype
         self.device = runner.device
+        self.token_capacity = runner.token_capacity  # the most tokens a step of this engine brings
         self.num_tokens = 0
         self.num_requests = 0
         self.max_q_len = 0

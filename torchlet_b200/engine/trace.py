@@ -29,7 +29,7 @@ def parse_args(argv=None):
                         help="most tokens live requests hold at any time (each rounded up to 64)")
     parser.add_argument("--page-size", type=int, default=16,
                         help="tokens per cache page (any size the kernels take)")
-    parser.add_argument("--max-live", type=int, default=8, help="most requests live at a time")
+    parser.add_argument("--max-live", type=int, default=4, help="most requests live at a time (state slots)")
     return parser.parse_args(argv)
 
 

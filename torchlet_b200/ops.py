@@ -46,7 +46,8 @@ _SIGNATURES = {
     },
     "attention_generic": {
         "tl_attention_generic": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
-                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_float, c_int,
+                                 c_void_p, c_int, c_void_p],
         "tl_attention_generic_debug_error": [c_void_p],
     },
     "gemm_tc": {
@@ -124,6 +125,30 @@ _SIGNATURES = {
                                     c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p,
                                     c_void_p, c_void_p],
         "tl_latent_attention_mma_debug_error": [c_void_p],
+    },
+    "gla": {
+        "tl_gla_decay": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
+        "tl_gla_scan": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                        c_int, c_float, c_void_p],
+        "tl_gla_finish": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
+                          c_void_p],
+        "tl_gla_debug_error": [c_void_p],
+    },
+    "gated_attention": {
+        "tl_normed_qk_store": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float, c_float, c_void_p, c_void_p,
+                               c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                               c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "tl_gated_attention_debug_error": [c_void_p],
+    },
+    "moe": {
+        "tl_moe_tile_rows": [],
+        "tl_moe_route": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                         c_void_p],
+        "tl_moe_plan": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "tl_moe_scatter": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "tl_moe_gemm_simt": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float,
+                             c_float, c_void_p],
+        "tl_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     },
     "sampling": {
         "tl_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -261,14 +286,18 @@ def gemm_simt(x, w, out, bias=None, accumulate=False) -> None:
 
 
 def attention_generic(q, q_stride, pages, block_table, token_req, positions, out, tokens, nh, nkv, d,
-                      page_size, window, scale) -> None:
-    """Paged causal GQA attention, one warp per (token, head); q may be a view into qkv."""
-    _need_cuda(q, pages, block_table, token_req, positions, out)
+                      page_size, window, scale, softcap=None, sink: bool = False, gate=None) -> None:
+    """Paged causal GQA attention, one warp per (token, head); q may be a view into qkv.
+    ``softcap``: scores become softcap * tanh(score / softcap); ``sink``: one is added to the softmax's
+    denominator; ``gate`` (float32 [tokens, >= nh * d] rows): the output is multiplied by sigmoid(gate)."""
+    _need_cuda(q, pages, block_table, token_req, positions, out, gate)
     assert q.dtype == pages.dtype == out.dtype and out.is_contiguous()
+    assert gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1)
     code = _fn("attention_generic", "tl_attention_generic")(
         q.data_ptr(), q_stride, pages.data_ptr(), dtype_code(q.dtype), block_table.data_ptr(),
         block_table.shape[1], token_req.data_ptr(), positions.data_ptr(), out.data_ptr(), out.stride(0),
-        tokens, nh, nkv, d, page_size, int(window or 0), float(scale), pages.shape[0], _stream())
+        tokens, nh, nkv, d, page_size, int(window or 0), float(scale), pages.shape[0], float(softcap or 0.0),
+        1 if sink else 0, _ptr(gate), gate.stride(0) if gate is not None else 0, _stream())
     _check(code, "attention_generic")
 
 
@@ -387,6 +416,129 @@ def delta_finish(o, proj, weight, out, heads: int, dim: int, eps: float) -> None
                                                 out.data_ptr(), dtype_code(out.dtype), tokens, heads, dim, float(eps),
                                                 _stream())
     _check(code, "delta_finish")
+
+
+# ----------------------------------------------------- gated linear attention
+def gla_decay(proj, low_offset: int, w2t, bias, decay, rank: int, tau: float) -> None:
+    """decay[t, c] = sigmoid(z)^(1 / tau), z = W2 proj[t, low_offset : low_offset + rank] + bias, float32
+    (csrc/gla.cu).  ``w2t`` is W2 TRANSPOSED, [rank, channels]."""
+    _need_cuda(proj, w2t, bias, decay)
+    tokens, channels = decay.shape
+    assert proj.dtype == w2t.dtype == bias.dtype == decay.dtype == torch.float32 and proj.stride(1) == 1
+    assert w2t.is_contiguous() and w2t.shape == (rank, channels) and decay.is_contiguous() and bias.numel() == channels
+    code = _fn("gla", "tl_gla_decay")(proj.data_ptr(), proj.stride(0), low_offset, w2t.data_ptr(), bias.data_ptr(),
+                                      decay.data_ptr(), tokens, channels, rank, float(tau), _stream())
+    _check(code, "gla_decay")
+
+
+def gla_scan(proj, decay, req_indptr, slots, state, out, requests: int, heads: int, dim: int, vdim: int,
+             qscale: float) -> None:
+    """Walks each request's tokens of the step through its slot's state [H, D, V] (float32):
+    S = diag(decay) S + k v^T, out = S^T q * qscale; ``proj`` rows are [q (H D) | k (H D) | v (H V) | ...].
+    A request whose slot is negative is padding."""
+    _need_cuda(proj, decay, req_indptr, slots, state, out)
+    assert proj.dtype == decay.dtype == state.dtype == out.dtype == torch.float32
+    assert state.is_contiguous() and out.is_contiguous() and decay.is_contiguous() and proj.stride(1) == 1
+    assert state.shape[1:] == (heads, dim, vdim) and req_indptr.dtype == slots.dtype == torch.int32
+    code = _fn("gla", "tl_gla_scan")(proj.data_ptr(), proj.stride(0), decay.data_ptr(), req_indptr.data_ptr(),
+                                     slots.data_ptr(), state.data_ptr(), out.data_ptr(), requests, heads, dim, vdim,
+                                     state.shape[0], float(qscale), _stream())
+    _check(code, "gla_scan")
+
+
+def gla_finish(o, proj, gate_offset: int, weight, out, heads: int, vdim: int, eps: float) -> None:
+    """out = o / rms(o per head) * weight * silu(g), g = proj[:, gate_offset:]; ``weight`` covers one head."""
+    _need_cuda(o, proj, weight, out)
+    tokens = o.shape[0]
+    assert o.dtype == weight.dtype == proj.dtype == torch.float32 and o.is_contiguous() and out.is_contiguous()
+    assert out.shape == o.shape == (tokens, heads * vdim) and weight.numel() == vdim
+    code = _fn("gla", "tl_gla_finish")(o.data_ptr(), proj.data_ptr(), proj.stride(0), gate_offset, weight.data_ptr(),
+                                       out.data_ptr(), dtype_code(out.dtype), tokens, heads, vdim, float(eps), _stream())
+    _check(code, "gla_finish")
+
+
+# ------------------------------------------- attention with normed queries and keys
+def normed_qk_store(proj, wq, wk, inv_freq, magnitude: float, eps: float, positions, token_req, block_table, pages,
+                    page_size: int, q_out, nh: int, nkv: int, d: int, dims: int, v_offset: int, write_kv: bool = True) -> None:
+    """From float32 projection rows [q (nh d) | k (nkv d) | ...]: RMS norm of the whole q and the whole k
+    (weights ``wq``, ``wk``; None: no norm), rotation of the first ``dims`` entries of every head, q to
+    ``q_out``, the key to plane 0 and proj[:, v_offset : v_offset + nkv d] to plane 1 of the cache rows
+    (csrc/gated_attention.cu)."""
+    _need_cuda(proj, wq, wk, inv_freq, positions, token_req, block_table, pages, q_out)
+    tokens = proj.shape[0]
+    assert proj.dtype == torch.float32 and proj.stride(1) == 1 and q_out.is_contiguous() and pages.is_contiguous()
+    assert q_out.shape == (tokens, nh * d) and pages.dtype == q_out.dtype
+    assert dims == 0 or (inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() == dims // 2)
+    code = _fn("gated_attention", "tl_normed_qk_store")(
+        proj.data_ptr(), proj.stride(0), _ptr(wq), _ptr(wk), _ptr(inv_freq), float(magnitude), float(eps),
+        positions.data_ptr(), token_req.data_ptr(), block_table.data_ptr(), block_table.shape[1], pages.data_ptr(),
+        dtype_code(q_out.dtype), page_size, pages.shape[0], q_out.data_ptr(), tokens, nh, nkv, d, dims,
+        1 if wq is not None else 0, 1 if wk is not None else 0, v_offset, 1 if write_kv else 0, _stream())
+    _check(code, "normed_qk_store")
+
+
+# ------------------------------------------------------- routed feed-forward
+def moe_tile_rows() -> int:
+    """Rows of a tile of the grouped CUDA-core products (every expert's rows are padded to whole tiles)."""
+    return _fn("moe", "tl_moe_tile_rows")()
+
+
+def moe_route(x, router, choice, weight, softmax_scores: bool = False, renormalize: bool = False) -> None:
+    """choice[t, j], weight[t, j]: the ``top`` experts of every token by score (sigmoid or softmax of the
+    float32 router logits) and their scores (csrc/moe.cu)."""
+    _need_cuda(x, router, choice, weight)
+    tokens, hidden = x.shape
+    experts, top = router.shape[0], choice.shape[1]
+    assert router.dtype == torch.float32 and router.is_contiguous() and router.shape[1] == hidden and x.stride(1) == 1
+    assert choice.dtype == torch.int32 and weight.dtype == torch.float32 and choice.is_contiguous() and weight.is_contiguous()
+    code = _fn("moe", "tl_moe_route")(x.data_ptr(), x.stride(0), dtype_code(x.dtype), router.data_ptr(), choice.data_ptr(),
+                                      weight.data_ptr(), tokens, hidden, experts, top, 1 if softmax_scores else 0,
+                                      1 if renormalize else 0, _stream())
+    _check(code, "moe_route")
+
+
+def moe_plan(choice, position, plan, experts: int, tile: int) -> None:
+    """position[t, j]: the row of (token, choice) in the expert-sorted order, every expert's rows padded to
+    whole tiles of ``tile`` rows; plan[0] tiles in use, plan[1 + i] the expert of tile i."""
+    _need_cuda(choice, position, plan)
+    assert position.dtype == plan.dtype == torch.int32 and position.numel() == choice.numel()
+    code = _fn("moe", "tl_moe_plan")(choice.data_ptr(), position.data_ptr(), plan.data_ptr(), choice.numel(), experts, tile,
+                                     plan.numel() - 1, _stream())
+    _check(code, "moe_plan")
+
+
+def moe_scatter(x, position, weight, out, top: int, weighted: bool) -> None:
+    """out[position[t, j]] = x[t] (* weight[t, j] if ``weighted``)."""
+    _need_cuda(x, position, weight, out)
+    tokens, hidden = x.shape
+    assert out.dtype == x.dtype and out.is_contiguous() and out.shape[1] == hidden and x.stride(1) == 1
+    code = _fn("moe", "tl_moe_scatter")(x.data_ptr(), x.stride(0), dtype_code(x.dtype), position.data_ptr(), weight.data_ptr(),
+                                        out.data_ptr(), tokens, hidden, top, 1 if weighted else 0, _stream())
+    _check(code, "moe_scatter")
+
+
+def moe_gemm_simt(x, w, out, plan, glu: bool = False, limit: float = 0.0, alpha: float = 0.0) -> None:
+    """Grouped product over expert-sorted rows on CUDA cores: out[r] = W_e(r) x[r]; ``w`` [experts, N, K], or
+    with ``glu`` [experts, 2 N, K] ([gate; up]) and the clamped gated activation applied."""
+    _need_cuda(x, w, out, plan)
+    rows, K = x.shape
+    N = out.shape[1]
+    assert x.is_contiguous() and w.is_contiguous() and out.is_contiguous() and w.dtype == x.dtype
+    assert w.shape[1:] == ((2 if glu else 1) * N, K) and rows == (plan.numel() - 1) * moe_tile_rows() == out.shape[0]
+    code = _fn("moe", "tl_moe_gemm_simt")(x.data_ptr(), w.data_ptr(), dtype_code(x.dtype), out.data_ptr(),
+                                          dtype_code(out.dtype), plan.data_ptr(), plan.numel() - 1, N, K, 1 if glu else 0,
+                                          float(limit), float(alpha), _stream())
+    _check(code, "moe_gemm_simt")
+
+
+def moe_combine(y, position, weight, side, top: int, weighted: bool) -> None:
+    """side[t] += sum_j y[position[t, j]] (* weight[t, j] if ``weighted``), float32, in the order of j."""
+    _need_cuda(y, position, weight, side)
+    tokens, hidden = side.shape
+    assert y.dtype == side.dtype == torch.float32 and y.is_contiguous() and side.is_contiguous() and y.shape[1] == hidden
+    code = _fn("moe", "tl_moe_combine")(y.data_ptr(), position.data_ptr(), weight.data_ptr(), side.data_ptr(), tokens,
+                                        hidden, top, 1 if weighted else 0, _stream())
+    _check(code, "moe_combine")
 
 
 # ------------------------------------------------------------ latent attention
@@ -769,7 +921,7 @@ def debug_errors() -> list:
     in the ordinary build (``TORCHLET_B200_DEBUG`` unset), whose kernels carry no checks."""
     found = []
     for library in ("elementwise", "attention_generic", "attention_mma", "decode_fused", "slots", "stream_ops",
-                    "delta_rule", "latent_attention", "latent_attention_mma"):
+                    "delta_rule", "latent_attention", "latent_attention_mma", "gla", "gated_attention"):
         if any(name in _functions for name in _SIGNATURES[library]):
             value = ctypes.c_int(0)
             code = _fn(library, f"tl_{library}_debug_error")(ctypes.byref(value))

@@ -28,7 +28,7 @@ class TensorSpec:
 
     name: str
     shape: tuple
-    init: str = "normal"  # "normal": N(0, std); "ones": 1 + N(0, norm_std)
+    init: str = "normal"  # "normal": N(0, std); "ones": 1 + N(0, norm_std); "zeros": N(0, norm_std)
     optional: bool = False
 
 
@@ -91,6 +91,12 @@ class Norm(Part):
         """Return the normed ``acc`` rows (all, or those ``rows`` names, int32) in the compute
         dtype; ``out`` or a buffer called ``name`` receives them."""
         raise NotImplementedError
+
+    def add_normed(self, ctx, y, acc, m: float = 1.0) -> None:
+        """acc += m * norm(y) in float32, for a norm that stands BEHIND a sub-layer (``y`` is the
+        float32 side stream the sub-layer added its output into).  Only norms that a block
+        arrangement uses in that place implement it."""
+        raise NotImplementedError(f"the norm {self.kind!r} cannot stand behind a sub-layer")
 
 
 class Positions(Part):

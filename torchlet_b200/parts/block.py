@@ -5,6 +5,8 @@
 float32; mixer and feed-forward add into it.
 
 "parallel_scaled": one norm, mixer and feed-forward side by side, a residual multiplier.
+
+"sandwich": a norm before and behind each sub-layer: x += norm_b(f(norm_a(x))).
 """
 from __future__ import annotations
 
@@ -46,3 +48,32 @@ class ParallelScaledBlock(Block):
         ops.scaled_add(acc, delta, m, cast)
         if token_input is not None:
             token_input.forward(ctx, acc, m, cast=cast)
+
+
+@BLOCKS.register("sandwich")
+class SandwichBlock(Block):
+    """x += post(mixer(pre(x))); then, if the layer has a feed-forward, x += post'(ff(pre'(x))).
+    Each sub-layer adds its output into a zeroed float32 stream of its own, the norm behind it
+    reads that stream and adds the normed rows into the residual stream (``Norm.add_normed``), so
+    the sub-layer's output, its norm and the residual sum are all float32."""
+
+    norm_roles = ("mixer_norm", "mixer_post_norm")
+
+    def __init__(self, mixer, feed_forward, norms, params=None, token_input=None):
+        super().__init__(mixer, feed_forward, norms, params, token_input)
+        if feed_forward is not None:
+            missing = [role for role in ("feed_forward_norm", "feed_forward_post_norm") if role not in norms]
+            if missing:
+                raise ValueError(f"block arrangement {self.kind!r} with a feed-forward needs norms for the roles {missing}")
+
+    def forward(self, ctx, acc, cache) -> None:
+        side = ctx.buffer("sandwich.side", tuple(acc.shape), acc.dtype)
+        x = self.norms["mixer_norm"].apply(ctx, acc)
+        ops.fill_zero(side)
+        self.mixer.forward(ctx, x, side, cache)
+        self.norms["mixer_post_norm"].add_normed(ctx, side, acc)
+        if self.feed_forward is not None:
+            x = self.norms["feed_forward_norm"].apply(ctx, acc)
+            ops.fill_zero(side)
+            self.feed_forward.forward(ctx, x, side)
+            self.norms["feed_forward_post_norm"].add_normed(ctx, side, acc)

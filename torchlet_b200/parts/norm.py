@@ -4,7 +4,11 @@
 Parameters: ``size``, ``eps``; ``groups`` (default 1): the row is split into that many equal
 consecutive parts and each is divided by its own root mean square, the weight covers the whole
 row; ``weight_name`` (default "weight"): the tensor's name below the norm's prefix ("" when the
-prefix itself is the tensor's name)."""
+prefix itself is the tensor's name); ``weight_offset`` (default 0): the stored weight lies around
+zero and the norm multiplies by ``weight_offset + w`` (1 for a "one plus weight" norm).
+
+``add_normed`` is the norm of a sub-layer's OUTPUT: acc += norm(y) for a float32 side stream y,
+one float32 kernel (a sandwich block's second norm)."""
 from __future__ import annotations
 
 import torch
@@ -21,17 +25,21 @@ class RMSNorm(Norm):
         self.size = int(spec.params["size"])
         self.eps = float(spec.params["eps"])
         self.groups = int(spec.params.get("groups", 1))
+        self.weight_offset = float(spec.params.get("weight_offset", 0.0))
         if self.groups <= 0 or self.size % self.groups:
             raise ValueError(f"a norm of {self.size} elements cannot be split into {self.groups} equal parts")
         self.weight = None
 
     @classmethod
     def expected_tensors(cls, spec: PartSpec, prefix: str) -> list[TensorSpec]:
-        return [TensorSpec(prefix + spec.params.get("weight_name", "weight"), (int(spec.params["size"]),), init="ones")]
+        init = "zeros" if float(spec.params.get("weight_offset", 0.0)) else "ones"
+        return [TensorSpec(prefix + spec.params.get("weight_name", "weight"), (int(spec.params["size"]),), init=init)]
 
     def load(self, tensors: dict, prefix: str, device, dtype) -> None:
         name = prefix + self.spec.params.get("weight_name", "weight")
         self.weight = tensors[name].to(device=device, dtype=torch.float32).contiguous()
+        if self.weight_offset:
+            self.weight += self.weight_offset
 
     fuses_pending = True  # a product's unfinished sum into the stream is completed in the norm's own kernel
 
@@ -49,3 +57,15 @@ class RMSNorm(Norm):
         ctx.flush_pending()
         ops.rms_norm(acc, self.weight, self.eps, out, rows, self.groups)
         return out
+
+    def add_normed(self, ctx, y, acc, m: float = 1.0) -> None:
+        """acc += m * norm(y): both float32 ``[T, size]``; ``y`` is a side stream a sub-layer added its
+        output into."""
+        if self.groups != 1:
+            raise ValueError("the norm of a sub-layer's output is not built for grouped norms")
+        pending = ctx.take_pending(y)
+        if pending is not None:  # the sub-layer's last product left its split sums: finish them into y first
+            ops.finish_accum_norm(pending.partials, pending.splits, pending.bias, y)
+        else:
+            ctx.flush_pending()
+        ops.rms_scaled_add(acc, y, self.weight, m, self.eps)

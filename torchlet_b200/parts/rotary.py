@@ -44,3 +44,54 @@ class RotarySplitHalf(Positions):
             return
         ops.rope_kv(qkv, ctx.positions, ctx.token_req, cache.block_table, cache.pages, self.inv_freq,
                     num_heads, num_kv_heads, self.head_dim, cache.page_size, write_kv=cache.writable)
+
+
+def scaled_frequencies(dims: int, base: float, scaling: dict | None) -> tuple:
+    """The rotation frequencies of ``dims`` rotated entries (dims / 2 pairs), f_i = base^(-2 i / dims), and
+    the magnitude both cos and sin are multiplied by.  With ``scaling`` (factor, original, fast, slow) the
+    frequencies are blended between f_i (pairs that turn fast: more than ``fast`` turns over ``original``
+    positions) and f_i / factor (pairs that turn slowly: fewer than ``slow`` turns): with
+    pair(turns) = dims ln(original / (2 pi turns)) / (2 ln base), lo = max(floor(pair(fast)), 0),
+    hi = min(ceil(pair(slow)), dims - 1), ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1),
+    f_i <- f_i / factor * ramp_i + f_i (1 - ramp_i); the magnitude is 0.1 ln(factor) + 1.
+    Taken in float64; returns (float64 tensor [dims / 2], float)."""
+    import math
+
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    freq = float(base) ** (-2.0 * i / dims)
+    if not scaling:
+        return freq, 1.0
+    factor, original = float(scaling["factor"]), float(scaling["original"])
+
+    def pair(turns: float) -> float:
+        return dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+
+    lo = max(math.floor(pair(float(scaling["fast"]))), 0)
+    hi = min(math.ceil(pair(float(scaling["slow"]))), dims - 1)
+    ramp = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+    freq = freq / factor * ramp + freq * (1.0 - ramp)
+    return freq, 0.1 * math.log(factor) + 1.0
+
+
+@POSITIONS.register("rotary_partial")
+class RotaryPartial(Positions):
+    """Split-half rotation of the FIRST ``dims`` entries of every head (entry i with i + dims / 2; the
+    rest pass unchanged), with optional frequency scaling (``scaled_frequencies``).  Parameters:
+    ``head_dim``, ``dims``, ``base``, ``scaling`` (None or factor / original / fast / slow).  The part
+    holds the table (``inv_freq``, float32) and the magnitude; the mixer that uses it rotates inside
+    its own kernel between its norm and its cache write (``ops.normed_qk_store``)."""
+
+    def __init__(self, spec: PartSpec):
+        super().__init__(spec)
+        self.head_dim = int(spec.params["head_dim"])
+        self.dims = int(spec.params["dims"])
+        self.base = float(spec.params["base"])
+        self.scaling = spec.params.get("scaling")
+        if self.dims % 2 or not 0 < self.dims <= self.head_dim:
+            raise ValueError(f"{self.dims} rotated entries do not fit a head of {self.head_dim}")
+        self.inv_freq = None
+        self.magnitude = 1.0
+
+    def load(self, tensors: dict, prefix: str, device, dtype) -> None:
+        freq, self.magnitude = scaled_frequencies(self.dims, self.base, self.scaling)
+        self.inv_freq = freq.to(torch.float32).to(device)

@@ -1,0 +1,95 @@
+"""A routed feed-forward (mixture of experts) of clamped gated units.
+
+Router: z = W_router x in float32, scores sigmoid(z) (``score`` "sigmoid") or softmax(z) ("softmax");
+every token uses the ``top_k`` experts with the largest scores (the lower index wins a tie); the
+weights are those scores, divided by their sum if ``renormalize``.  Expert e: g = min(W_gate,e h, limit),
+u = clamp(W_up,e h, -limit, limit), y = g sigmoid(alpha g) (u + 1), output W_down,e y, no biases.  The
+weight multiplies the expert's INPUT (``weight_on`` "input": out = sum_j expert_j(w_j x)) or its output
+("output": out = sum_j w_j expert_j(x)).
+
+Routing, the expert-sorted order and the products are planned and run on the device (csrc/moe.cu):
+nothing is read back, so steps of single tokens are captured like any other part's.
+
+Parameters: ``hidden_size``, ``intermediate_size``, ``limit``, ``alpha``, ``num_experts``, ``top_k``,
+``score``, ``renormalize``, ``weight_on``.  Tensors below the prefix: router [E, hidden];
+e<j>.gate, e<j>.up [ff, hidden]; e<j>.down [hidden, ff].
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..config.spec import PartSpec
+from .base import FEED_FORWARDS, FeedForward, TensorSpec
+
+
+@FEED_FORWARDS.register("routed_clamped_glu")
+class RoutedClampedGLU(FeedForward):
+    def __init__(self, spec: PartSpec):
+        super().__init__(spec)
+        p = spec.params
+        self.hidden_size = int(p["hidden_size"])
+        self.intermediate_size = int(p["intermediate_size"])
+        self.limit = float(p["limit"])
+        self.alpha = float(p.get("alpha", 1.702))
+        self.num_experts = int(p["num_experts"])
+        self.top_k = int(p["top_k"])
+        self.score = p.get("score", "sigmoid")
+        self.renormalize = bool(p.get("renormalize", False))
+        self.weight_on = p.get("weight_on", "output")
+        if self.score not in ("sigmoid", "softmax"):
+            raise ValueError(f"unknown router score {self.score!r} (known: sigmoid, softmax)")
+        if self.weight_on not in ("input", "output"):
+            raise ValueError(f"weight_on must be 'input' or 'output', got {self.weight_on!r}")
+        if not 0 < self.top_k <= self.num_experts:
+            raise ValueError(f"top_k {self.top_k} does not fit {self.num_experts} experts")
+        if self.num_experts > 256:
+            raise ValueError("the router kernel takes up to 256 experts")
+        self.router = self.gate_up = self.down = None
+
+    @classmethod
+    def expected_tensors(cls, spec: PartSpec, prefix: str) -> list[TensorSpec]:
+        p = spec.params
+        hidden, inter, experts = int(p["hidden_size"]), int(p["intermediate_size"]), int(p["num_experts"])
+        out = []
+        for e in range(experts):
+            out += [TensorSpec(f"{prefix}e{e}.gate", (inter, hidden)), TensorSpec(f"{prefix}e{e}.up", (inter, hidden)),
+                    TensorSpec(f"{prefix}e{e}.down", (hidden, inter))]
+        out.append(TensorSpec(prefix + "router", (experts, hidden)))
+        return out
+
+    def load(self, tensors: dict, prefix: str, device, dtype) -> None:
+        E = self.num_experts
+        self.router = tensors[prefix + "router"].to(device=device, dtype=torch.float32).contiguous()
+        # per expert [gate; up] stacked, [E, 2 ff, hidden], and [E, hidden, ff]
+        self.gate_up = torch.stack([torch.cat([tensors[f"{prefix}e{e}.gate"], tensors[f"{prefix}e{e}.up"]], dim=0)
+                                    for e in range(E)]).to(device=device, dtype=dtype).contiguous()
+        self.down = torch.stack([tensors[f"{prefix}e{e}.down"] for e in range(E)]).to(device=device, dtype=dtype).contiguous()
+
+    def _rows(self, tokens: int, tile: int) -> tuple:
+        """(row tiles, rows) the expert-sorted order of ``tokens`` tokens can take at most: every
+        expert's rows are padded to whole tiles."""
+        entries = tokens * self.top_k
+        tiles = entries // tile + min(self.num_experts, entries)
+        return tiles, tiles * tile
+
+    def forward(self, ctx, x, acc) -> None:
+        tokens, top, E = x.shape[0], self.top_k, self.num_experts
+        tile = ops.moe_tile_rows()
+        tiles, rows = self._rows(tokens, tile)
+        # scratch sized once for the largest step, so that its addresses never change
+        most_tiles, most_rows = self._rows(max(ctx.token_capacity, tokens), tile)
+        choice = ctx.buffer("moe.choice", (tokens, top), torch.int32)
+        weight = ctx.buffer("moe.weight", (tokens, top), torch.float32)
+        position = ctx.buffer("moe.position", (tokens, top), torch.int32)
+        plan = ctx.buffer("moe.plan", (most_tiles + 1,), torch.int32)[:tiles + 1]
+        sorted_x = ctx.buffer("moe.sorted", (most_rows, self.hidden_size), ctx.dtype)[:rows]
+        act = ctx.buffer("moe.act", (most_rows, self.intermediate_size), ctx.dtype)[:rows]
+        y = ctx.buffer("moe.y", (most_rows, self.hidden_size), torch.float32)[:rows]
+        on_input = self.weight_on == "input"
+        ops.moe_route(x, self.router, choice, weight, self.score == "softmax", self.renormalize)
+        ops.moe_plan(choice, position, plan, E, tile)
+        ops.moe_scatter(x, position, weight, sorted_x, top, weighted=on_input)
+        ops.moe_gemm_simt(sorted_x, self.gate_up, act, plan, glu=True, limit=self.limit, alpha=self.alpha)
+        ops.moe_gemm_simt(act, self.down, y, plan)
+        ops.moe_combine(y, position, weight, acc, top, weighted=not on_input)

@@ -194,6 +194,53 @@ def test_attention_with_cap_sink_and_window_on_designed_keys(dtype, window, page
     close(out.view(len(rows), H, d), want[rows], 2e-5 if dtype == "float32" else 2e-2, "attention")
 
 
+@pytest.mark.parametrize("d,H,G", [(64, 4, 1), (128, 6, 2), (64, 2, 2)])
+@pytest.mark.parametrize("window,page_size", [(150, 16), (70, 16), (64, 8), (None, 16), (1, 16)])
+@pytest.mark.parametrize("softcap,sink,gated", [(20.0, True, True), (None, True, False), (30.0, False, False)])
+def test_tensor_core_attention_with_cap_sink_gate_equals_the_plain_kernel(d, H, G, window, page_size, softcap, sink, gated):
+    """The mma.sync kernel (64-row tiles for a prompt portion, 16-row tiles with 1, 3 and 20 key splits for a
+    single token, merged inside the kernel and by the second kernel) against the one-warp-a-row kernel on the
+    same pages, with two designed keys at the window's edge."""
+    from torchlet_b200 import ops
+
+    T, scale, g = 700, d ** -0.5, H // G
+    td = torch.bfloat16
+    k = rand(T, G, d, seed=21, scale=0.5)
+    v = rand(T, G, d, seed=22, scale=0.5)
+    q = rand(T, H, d, seed=23, scale=0.5)
+    last = T - 1
+    if window and window > 1:
+        k[last - window + 1, :, 5] = 9.0
+        k[last - window, :, 6] = 9.0
+        q[last, :, 5:7] = 6.0
+    pages, table = _paged(k, v, page_size, td, seed=d + page_size)
+    gate = rand(T, H * d + 3, seed=24, scale=2.0).to(DEV) if gated else None
+    gate_view = gate[:, 3:] if gated else None
+    qd = q.reshape(T, H * d).to(td).to(DEV)
+    pos = torch.arange(T, dtype=torch.int32, device=DEV)
+    zeros = torch.zeros(T, dtype=torch.int32, device=DEV)
+    want = torch.empty(T, H * d, dtype=td, device=DEV)
+    ops.attention_generic(qd, H * d, pages, table, zeros, pos, want, T, H, G, d, page_size, window, scale, softcap=softcap,
+                          sink=sink, gate=gate_view)
+    # the whole prompt as one portion, 64 packed rows a tile
+    rows = torch.arange(0, T * g, 64, dtype=torch.int32, device=DEV)
+    indptr = torch.tensor([0, T], dtype=torch.int32, device=DEV)
+    before = torch.zeros(1, dtype=torch.int32, device=DEV)
+    got = torch.full((T, H * d), float("nan"), dtype=td, device=DEV)
+    ops.attention_mma(qd, pages, table, indptr, before, torch.zeros_like(rows), rows, rows.numel(), got, T, H, G, d, page_size,
+                      window, scale, rows16=False, softcap=softcap, sink=sink, gate=gate_view)
+    close(got, want.float().cpu(), 2e-2, "prompt portion")
+    # the last token alone, behind 699 cached ones
+    indptr = torch.tensor([0, 1], dtype=torch.int32, device=DEV)
+    before = torch.tensor([last], dtype=torch.int32, device=DEV)
+    for splits in (1, 3, 20):
+        one = torch.full((1, H * d), float("nan"), dtype=td, device=DEV)
+        ops.attention_mma(qd[last:], pages, table, indptr, before, None, None, 1, one, 1, H, G, d, page_size, window, scale,
+                          rows16=True, splits=splits, softcap=softcap, sink=sink,
+                          gate=gate_view[last:] if gated else None)
+        close(one, want[last:].float().cpu(), 2e-2, f"single token, {splits} key splits")
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_attention_output_gate(dtype):
     from torchlet_b200 import ops
@@ -272,7 +319,8 @@ def _moe_weights(E, width, ff, seed):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("E,top,width,ff,tokens", [(5, 2, 96, 40, 150), (1, 1, 64, 24, 7), (3, 3, 64, 24, 33),
-                                                   (8, 1, 72, 100, 300), (16, 4, 128, 64, 1), (6, 2, 50, 21, 70)])
+                                                   (8, 1, 72, 100, 300), (16, 4, 128, 64, 1), (6, 2, 50, 21, 70),
+                                                   (4, 2, 128, 64, 500), (7, 3, 256, 320, 900), (32, 1, 64, 48, 20)])
 def test_routed_feed_forward_on_given_inputs(dtype, E, top, width, ff, tokens):
     """The whole part on inputs that BOTH sides hold exactly (rounded to the engine's type first), so the
     choice of experts is the same unless two scores tie; the limit is low enough to clamp many entries."""

@@ -67,7 +67,24 @@ struct Params {
   int overlap_max_tiles;  // host only: overlapped launch up to this many row tiles
   int late_wait;  // the kernel before this one has itself waited for q, keys and values: start at once, wait for it at the end
   float scale_log2;  // scale * log2(e)
+  // options: a score cap, s <- cap tanh(s / cap) (cap_inner = scale / cap, cap_outer = cap * log2(e); 0: off);
+  // a sink (one more in the softmax's denominator: a key of score 0 without a value); an output gate
+  // (float32 rows [tokens][>= nh D]: the output is multiplied by sigmoid(gate))
+  float cap_inner, cap_outer;
+  int sink;
+  const float* gate;
+  long long gate_stride;
 };
+
+__device__ __forceinline__ float capped_tanh(float x) { return 1.f - 2.f / (__expf(2.f * x) + 1.f); }
+// The softmax denominator with the sink's share: a key of score 0 against the running maximum m (log2 units).
+__device__ __forceinline__ float with_sink(const Params& p, float l, float m) {
+  return (p.sink && m != -INFINITY) ? l + exp2f(-m) : l;
+}
+__device__ __forceinline__ float gate_of(const Params& p, int token, int head, int D, int c) {
+  if (!p.gate) return 1.f;
+  return 1.f / (1.f + __expf(-p.gate[(size_t)token * p.gate_stride + (size_t)head * D + c]));
+}
 
 __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
   const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -416,7 +433,10 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p)
         const int h = e >> 1;
         const int key = key_base + i * 8 + (lane & 3) * 2 + (e & 1);
         const bool ok = key <= row_pos[h] && key >= row_lo[h];
-        s[i][e] = ok ? s[i][e] * p.scale_log2 : -INFINITY;
+        if (p.cap_outer > 0.f)
+          s[i][e] = ok ? capped_tanh(s[i][e] * p.cap_inner) * p.cap_outer : -INFINITY;
+        else
+          s[i][e] = ok ? s[i][e] * p.scale_log2 : -INFINITY;
         tile_max[h] = fmaxf(tile_max[h], s[i][e]);
       }
     }
@@ -533,7 +553,8 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p)
           p.part_ml[item * 2 + 1] = l;
         }
       } else {
-        p.out[(size_t)token * p.out_stride + (size_t)head * D + c] = __float2bfloat16_rn(acc / l);
+        p.out[(size_t)token * p.out_stride + (size_t)head * D + c] =
+            __float2bfloat16_rn(acc / with_sink(p, l, m_all) * gate_of(p, token, head, D, c));
       }
     }
     if (p.splits > 1 && p.arrivals) {
@@ -586,7 +607,14 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p)
               acc.w = fmaf(v[j].w, f, acc.w);
             }
           }
-          const float inv = 1.f / l;
+          const float inv = 1.f / with_sink(p, l, m_ref);
+          if (p.gate) {
+            const int head = kvh * g + r;
+            acc.x *= gate_of(p, tok0, head, D, c);
+            acc.y *= gate_of(p, tok0, head, D, c + 1);
+            acc.z *= gate_of(p, tok0, head, D, c + 2);
+            acc.w *= gate_of(p, tok0, head, D, c + 3);
+          }
           uint2 packed;
           packed.x = pack_bf16(acc.x * inv, acc.y * inv);
           packed.y = pack_bf16(acc.z * inv, acc.w * inv);
@@ -600,11 +628,13 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p)
       const int row = row_start + my_rows + (lane >> 2) + 8 * h;
       if (row >= row_end) continue;
       const int token = tok0 + row / g, head = kvh * g + row % g;
-      const float inv = 1.f / l_run[h];
+      const float inv = 1.f / with_sink(p, l_run[h], m_run[h]);
       __nv_bfloat16* dst = p.out + (size_t)token * p.out_stride + (size_t)head * D + (lane & 3) * 2;
 #pragma unroll
       for (int i = 0; i < DTILES; ++i) {
-        *reinterpret_cast<unsigned*>(dst + i * 8) = pack_bf16(o_acc[i][2 * h] * inv, o_acc[i][2 * h + 1] * inv);
+        const int c = i * 8 + (lane & 3) * 2;
+        *reinterpret_cast<unsigned*>(dst + i * 8) = pack_bf16(o_acc[i][2 * h] * inv * gate_of(p, token, head, D, c),
+                                                              o_acc[i][2 * h + 1] * inv * gate_of(p, token, head, D, c + 1));
       }
     }
   }
@@ -621,7 +651,8 @@ __global__ void __launch_bounds__(D)
 attention_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                          const int* __restrict__ tile_req, const int* __restrict__ req_indptr,
                          const int* __restrict__ kv_before, int window,
-                         __nv_bfloat16* __restrict__ out, long long out_stride, int nh, int grid_splits) {
+                         __nv_bfloat16* __restrict__ out, long long out_stride, int nh, int grid_splits, int sink,
+                         const float* __restrict__ gate, long long gate_stride) {
   tl::pdl_launch_dependents();  // the next kernel may start its prologue (it waits for us before it reads our output)
   tl::pdl_wait();               // everything before us in the stream is complete and visible
 
@@ -646,6 +677,7 @@ attention_combine_kernel(const float* __restrict__ part_acc, const float* __rest
     weight[c + 32] = f1;
     float l = (c < splits ? ml[2 * c + 1] * f0 : 0.f) + (c + 32 < splits ? ml[2 * (c + 32) + 1] * f1 : 0.f);
     l = tl::warp_sum(l);
+    if (sink && m_all != -INFINITY) l += exp2f(-m_ref);  // the sink's share of the denominator
     if (c == 0) total[0] = l;
   }
   __syncthreads();
@@ -661,7 +693,9 @@ attention_combine_kernel(const float* __restrict__ part_acc, const float* __rest
   }
   for (; s < splits; ++s) acc = fmaf(src[(size_t)s * D], weight[s], acc);
   const int token = req_indptr[req];
-  out[(size_t)token * out_stride + (size_t)head * D + c] = __float2bfloat16_rn(acc / total[0]);
+  float result = acc / total[0];
+  if (gate) result *= 1.f / (1.f + __expf(-gate[(size_t)token * gate_stride + (size_t)head * D + c]));
+  out[(size_t)token * out_stride + (size_t)head * D + c] = __float2bfloat16_rn(result);
 }
 
 // Tensor maps of cache layers [rows][D] with boxes of page_size x 64 elements, by base address.
@@ -797,12 +831,15 @@ int tl_attention_mma_error() {
 // portions' attention (tl_attention_tc), which neither reads nor writes anything this call writes;
 // this grid then starts beside it on the SMs it leaves idle and waits for it only at its end.
 // pages: one cache layer [num_pages][2][nkv][page_size][d].
-int tl_attention_mma(const void* q, long long q_stride, const void* pages, long long num_pages, const int* block_table,
-                     int table_width,
-                     const int* req_indptr, const int* kv_before, const int* tile_req, const int* tile_row,
-                     int tiles, void* out, long long out_stride, int tokens, int nh, int nkv, int d, int page_size,
-                     int window, float scale, int rows16, int splits, void* workspace, long long workspace_bytes,
-                     int* arrivals, int late_wait, cudaStream_t stream) {
+// softcap > 0: scores are capped, s <- softcap tanh(s / softcap); sink: one is added to the softmax's
+// denominator; gate (float32 [tokens][gate_stride], or null): the output is multiplied by sigmoid(gate).
+int tl_attention_mma_ex(const void* q, long long q_stride, const void* pages, long long num_pages, const int* block_table,
+                        int table_width,
+                        const int* req_indptr, const int* kv_before, const int* tile_req, const int* tile_row,
+                        int tiles, void* out, long long out_stride, int tokens, int nh, int nkv, int d, int page_size,
+                        int window, float scale, int rows16, int splits, void* workspace, long long workspace_bytes,
+                        int* arrivals, int late_wait, float softcap, int sink, const float* gate, long long gate_stride,
+                        cudaStream_t stream) {
   if (tiles <= 0 || tokens <= 0) return 0;
   if ((d != 64 && d != 128) || nkv <= 0 || nh % nkv || page_size <= 0 || q_stride % 8 || out_stride % 4)
     return TL_ERR_UNSUPPORTED;
@@ -836,17 +873,33 @@ int tl_attention_mma(const void* q, long long q_stride, const void* pages, long 
   p.window = window;
   p.splits = splits;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.cap_inner = softcap > 0.f ? scale / softcap : 0.f;
+  p.cap_outer = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
+  p.sink = sink;
+  p.gate = gate;
+  p.gate_stride = gate_stride;
   const int rc = d == 128 ? launch_for<128>(p, num_pages, tiles, rows16 != 0, stream)
                            : launch_for<64>(p, num_pages, tiles, rows16 != 0, stream);
   if (rc || splits == 1 || arrivals) return rc;
   const int items = tiles * nh;
   if (d == 128)
     tl::launch_kernel(attention_combine_kernel<128>, items, 128, 0, stream, p.part_acc, p.part_ml, tile_req, req_indptr,
-                      kv_before, window, p.out, out_stride, nh, splits);
+                      kv_before, window, p.out, out_stride, nh, splits, sink, gate, gate_stride);
   else
     tl::launch_kernel(attention_combine_kernel<64>, items, 64, 0, stream, p.part_acc, p.part_ml, tile_req, req_indptr,
-                      kv_before, window, p.out, out_stride, nh, splits);
+                      kv_before, window, p.out, out_stride, nh, splits, sink, gate, gate_stride);
   return TL_LAUNCH_CHECK();
+}
+
+int tl_attention_mma(const void* q, long long q_stride, const void* pages, long long num_pages, const int* block_table,
+                     int table_width,
+                     const int* req_indptr, const int* kv_before, const int* tile_req, const int* tile_row,
+                     int tiles, void* out, long long out_stride, int tokens, int nh, int nkv, int d, int page_size,
+                     int window, float scale, int rows16, int splits, void* workspace, long long workspace_bytes,
+                     int* arrivals, int late_wait, cudaStream_t stream) {
+  return tl_attention_mma_ex(q, q_stride, pages, num_pages, block_table, table_width, req_indptr, kv_before, tile_req,
+                             tile_row, tiles, out, out_stride, tokens, nh, nkv, d, page_size, window, scale, rows16, splits,
+                             workspace, workspace_bytes, arrivals, late_wait, 0.f, 0, nullptr, 0, stream);
 }
 
 }  // extern "C"

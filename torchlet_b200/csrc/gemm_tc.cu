@@ -60,6 +60,11 @@ struct Params {
   // the gated epilogue: limit 0: silu(gate) * up; limit > 0: g = min(gate, limit), u = clamp(up, +-limit),
   // g * sigmoid(alpha g) * (u + 1)
   float glu_limit, glu_alpha;
+  // grouped product (persistent kernel): row tile i belongs to ONE group, plan[1 + i] (plan[0] tiles are in
+  // use; a negative group or a tile past plan[0] is skipped); group g's weights are rows
+  // [g group_rows, (g + 1) group_rows) of the column operand.  nullptr: one group.
+  const int* plan;
+  int group_rows;
 };
 
 __device__ __forceinline__ float silu(float g) { return g / (1.f + __expf(-g)); }
@@ -376,6 +381,14 @@ gemm_tc_swapped_kernel(const __grid_constant__ CUtensorMap map_row, const __grid
   }
 }
 
+// The group of a tile of the persistent kernel (0 without a plan); negative: the tile is skipped.  Every
+// role of the CTA asks with the same arguments, so all of them skip the same tiles.
+__device__ __forceinline__ int tile_group(const Params& p, int tile) {
+  if (!p.plan) return 0;
+  const int row_tile = tile % p.row_tiles;
+  return row_tile < p.plan[0] ? p.plan[1 + row_tile] : -1;
+}
+
 // Normal orientation, persistent: one CTA per SM walks over output tiles (row tiles
 // fastest, so CTAs running at the same time share weight tiles in L2).  The tile width
 // block_q (a multiple of 16 up to 256) is chosen on the host so that the tiles fill whole
@@ -429,13 +442,16 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_row, const __g
       int s = 0;
       uint32_t phase = 0;
       for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
+        const int group = tile_group(p, tile);
+        if (group < 0) continue;
         const int row0 = (tile % p.row_tiles) * BLOCK_P, col0 = (tile / p.row_tiles) * p.block_q;
+        const int wrow0 = group * p.group_rows + col0;
         for (int kb = 0; kb < num_kb; ++kb) {
           mbar_wait(&empty[s], phase ^ 1, abort_flag, &g_error_word, 1);
           mbar_expect_tx(&full[s], stage_bytes);
           uint8_t* stage = smem + s * stage_bytes;
           tma_load_2d(stage, &map_row, &full[s], kb * BLOCK_K, row0);
-          tma_load_2d(stage + ROW_TILE_BYTES, &map_col, &full[s], kb * BLOCK_K, col0);
+          tma_load_2d(stage + ROW_TILE_BYTES, &map_col, &full[s], kb * BLOCK_K, wrow0);
           if (++s == p.stages) {
             s = 0;
             phase ^= 1;
@@ -455,7 +471,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_row, const __g
     int s = 0, local = 0;
     uint32_t phase = 0;
     uint64_t a_desc = a_desc0, b_desc = b_desc0;
-    for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++local) {
+    for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
+      if (tile_group(p, tile) < 0) continue;
       const int a = local & 1;
       mbar_wait(&tmem_empty[a], ((local >> 1) & 1) ^ 1, abort_flag, &g_error_word, 4);
       const uint32_t acc = tmem_base + a * ACC_COLS;
@@ -478,11 +495,13 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_row, const __g
           b_desc = b_desc0;
         }
       }
+      ++local;
     }
   } else {
     const int quarter = warp & 3;
     int local = 0;
-    for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++local) {
+    for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
+      if (tile_group(p, tile) < 0) continue;
       const int a = local & 1;
       const int row0 = (tile % p.row_tiles) * BLOCK_P, col0 = (tile / p.row_tiles) * p.block_q;
       mbar_wait(&tmem_full[a], (local >> 1) & 1, abort_flag, &g_error_word, 3);
@@ -517,6 +536,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_row, const __g
       fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[a]);
+      ++local;
     }
   }
   fence_before_sync();
@@ -1012,6 +1032,8 @@ static int gemm_tc_impl(const void* x, const void* w, const float* bias, void* o
   p.ahead = 8;  // all stages
   p.glu_limit = glu_limit;
   p.glu_alpha = glu_alpha;
+  p.plan = nullptr;
+  p.group_rows = 0;
   if (splits_out) *splits_out = 0;
   CUtensorMap map_row, map_col;
   int rc;
@@ -1109,6 +1131,57 @@ static int gemm_tc_impl(const void* x, const void* w, const float* bias, void* o
     return TL_ERR_UNSUPPORTED;
   p.block_q = block_q;
   p.row_tiles = (M + BLOCK_P - 1) / BLOCK_P;
+  p.num_tiles = p.row_tiles * ((N + block_q - 1) / block_q);
+  const int stage_bytes = ROW_TILE_BYTES + block_q * BLOCK_K * 2;
+  p.stages = (SMEM_LIMIT - 1024 - 512) / stage_bytes;
+  if (p.stages > 8) p.stages = 8;
+  const int smem = p.stages * stage_bytes + 1024 + 512;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t err = cudaFuncSetAttribute(gemm_tc_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           SMEM_LIMIT);
+    if (err != cudaSuccess) return (int)err;
+    configured = true;
+  }
+  const int ctas = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
+  tl::launch_kernel(gemm_tc_persistent_kernel, dim3(ctas), THREADS, smem, stream, map_row, map_col, p);
+  return TL_LAUNCH_CHECK();
+}
+
+// Grouped product over group-sorted rows: x [rows, K] (rows a multiple of 128; row tile i belongs to group
+// plan[1 + i], plan[0] tiles are in use), w [groups * N, K] (group g's matrix in rows [g N, (g + 1) N)),
+// out [rows, N] (or [rows, N / 2] with the gated epilogue over 16-interleaved gate / up rows).  The plan is
+// read on the device, so nothing comes back to the host; tiles that are not in use cost nothing.
+int tl_gemm_tc_grouped(const void* x, const void* w, void* out, long long ldo, int epilogue, int rows, int N, int K,
+                       int groups, const int* plan, float glu_limit, float glu_alpha, cudaStream_t stream) {
+  if (rows <= 0 || N <= 0 || groups <= 0) return 0;
+  if (K <= 0 || K % 8 || rows % BLOCK_P || !plan || epilogue < 0 || epilogue > 3) return TL_ERR_UNSUPPORTED;
+  if (epilogue == EPI_SWIGLU_BF16 && N % 32) return TL_ERR_UNSUPPORTED;
+  if (epilogue == EPI_ACCUM_F32) return TL_ERR_UNSUPPORTED;
+  Params p;
+  p.k_blocks = p.k_blocks_per_split = (K + BLOCK_K - 1) / BLOCK_K;
+  p.bias = nullptr;
+  p.out = out;
+  p.ldo = ldo;
+  p.epilogue = epilogue;
+  p.partial = nullptr;
+  p.splits = 1;
+  p.ahead = 8;
+  p.glu_limit = glu_limit;
+  p.glu_alpha = glu_alpha;
+  p.plan = plan;
+  p.group_rows = N;
+  p.rows = rows;
+  p.cols = N;
+  int block_q = 256;
+  best_width(rows, N, false, &block_q);
+  if (epilogue == EPI_SWIGLU_BF16) block_q = (block_q + 31) / 32 * 32 > 256 ? 256 : (block_q + 31) / 32 * 32;
+  CUtensorMap map_row, map_col;
+  if (!cached_map(&map_row, x, rows, K, K, BLOCK_P) || !cached_map(&map_col, w, (uint64_t)groups * N, K, K, block_q))
+    return TL_ERR_UNSUPPORTED;
+  constexpr int SMEM_LIMIT = 227 * 1024;
+  p.block_q = block_q;
+  p.row_tiles = rows / BLOCK_P;
   p.num_tiles = p.row_tiles * ((N + block_q - 1) / block_q);
   const int stage_bytes = ROW_TILE_BYTES + block_q * BLOCK_K * 2;
   p.stages = (SMEM_LIMIT - 1024 - 512) / stage_bytes;

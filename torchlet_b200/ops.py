@@ -55,6 +55,8 @@ _SIGNATURES = {
                        c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p],
         "tl_gemm_tc_glu": [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_longlong, c_longlong, c_void_p,
                            c_longlong, c_float, c_float, c_void_p],
+        "tl_gemm_tc_grouped": [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float,
+                               c_float, c_void_p],
         "tl_gemm_tc_plan": [c_int, c_int, c_int, c_void_p, c_void_p],
         "tl_gemm_tc_error": [],
         "tl_gemm_tc_wait_selftest": [c_int, c_void_p],
@@ -63,6 +65,10 @@ _SIGNATURES = {
         "tl_attention_mma": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                              c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                              c_int, c_int, c_void_p, c_longlong, c_void_p, c_int, c_void_p],
+        "tl_attention_mma_ex": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                c_int, c_int, c_void_p, c_longlong, c_void_p, c_int, c_float, c_int, c_void_p, c_longlong,
+                                c_void_p],
         "tl_attention_mma_error": [],
         "tl_attention_mma_debug_error": [c_void_p],
     },
@@ -749,6 +755,33 @@ def gemm_tc_glu(x, w, out, limit: float, alpha: float) -> None:
     _check(code, "gemm_tc_glu", 2 if need and splits > 1 else 1)
 
 
+GROUPED_TILE_ROWS = 128  # rows of a tile of the grouped tcgen05 product: every group's rows are padded to these
+
+
+def gemm_tc_grouped(x, w, out, plan, glu: bool = False, limit: float = 0.0, alpha: float = 0.0) -> None:
+    """Grouped product over group-sorted rows on the tcgen05 tensor cores (the persistent kernel of
+    csrc/gemm_tc.cu with a plan): out[r] = W_g(r) x[r].  ``x`` [rows, K] bfloat16 with rows = 128 * tiles;
+    ``plan`` int32 [1 + tiles] on the device: plan[0] tiles in use, plan[1 + i] the group of row tile i;
+    ``w`` [groups, N, K]; ``out`` [rows, N] float32 or bfloat16, or with ``glu`` (``w`` [groups, 2 F, K], gate
+    and up rows interleaved by 16) [rows, F] bfloat16 with the clamped gated activation applied."""
+    _need_cuda(x, w, out, plan)
+    _release_workspace()
+    rows, K = x.shape
+    groups, N = w.shape[0], w.shape[1]
+    assert x.dtype == w.dtype == torch.bfloat16 and x.is_contiguous() and w.is_contiguous() and w.shape[2] == K
+    assert rows == (plan.numel() - 1) * GROUPED_TILE_ROWS == out.shape[0] and plan.dtype == torch.int32
+    assert out.stride(1) == 1 and out.shape[1] == (N // 2 if glu else N)
+    if glu:
+        assert out.dtype == torch.bfloat16
+        epilogue = EPI_SWIGLU_BF16
+    else:
+        epilogue = EPI_STORE_BF16 if out.dtype == torch.bfloat16 else EPI_STORE_F32
+    code = _fn("gemm_tc", "tl_gemm_tc_grouped")(
+        x.data_ptr(), w.data_ptr(), out.data_ptr(), out.stride(0), epilogue, rows, N, K, groups, plan.data_ptr(),
+        float(limit), float(alpha), _stream())
+    _check(code, "gemm_tc_grouped")
+
+
 def gemm_tc_deferred(x, w):
     """The product x @ w.T left as float32 partial sums ``[splits, M, N]`` for a fused
     finishing kernel.  Returns (partials, splits), or None when the sizes run in a
@@ -827,16 +860,20 @@ _merge_in_kernel = os.environ.get("TORCHLET_B200_DECODE_MERGE", "") != "kernel"
 
 
 def attention_mma(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile_row, tiles, out, tokens, nh, nkv,
-                  d, page_size, window, scale, rows16: bool, splits: int = 1, late_wait: bool = False) -> None:
+                  d, page_size, window, scale, rows16: bool, splits: int = 1, late_wait: bool = False,
+                  softcap=None, sink: bool = False, gate=None) -> None:
     """Tensor-core paged attention (csrc/attention_mma.cu).  ``tile_req``/``tile_row`` None:
     tile i is request i from its first packed row.  With ``splits`` > 1 every tile is a request
     that brings one token; only those tokens' rows of ``out`` are written.  ``splits`` is the
     number of CTAs the grid holds for a request's keys; the kernel uses as many as the request's
     own length warrants.  ``late_wait`` (16-row tiles): the launch just before this one on the
     stream was ``attention_tc`` for the other requests of the same step; this grid starts beside
-    it and waits for it at its end instead of at its start."""
-    _need_cuda(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile_row, out)
+    it and waits for it at its end instead of at its start.  ``softcap``: scores become
+    softcap * tanh(score / softcap); ``sink``: one is added to the softmax's denominator; ``gate`` (float32
+    rows [tokens, >= nh * d]): the output is multiplied by sigmoid(gate)."""
+    _need_cuda(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile_row, out, gate)
     assert qkv.dtype == pages.dtype == out.dtype == torch.bfloat16
+    assert gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1)
     # key splits: float32 partial results of every (decode tile, head, split); the split that finishes last merges
     need = tiles * nh * splits * (d + 2) * 4 if splits > 1 else 0
     ws = _workspace(("attention", qkv.device), need) if need else None
@@ -844,12 +881,13 @@ def attention_mma(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile
     # measured -1 % of a decode step at batch 8 to 32); more are merged by a second kernel, whose
     # many small CTAs do better than one CTA's two rounds (batch 1 at 4,096 tokens: 32 splits)
     arrivals = _arrivals(qkv.device, tiles * nkv) if need and _merge_in_kernel and splits <= 16 else None
-    code = _fn("attention_mma", "tl_attention_mma")(
+    code = _fn("attention_mma", "tl_attention_mma_ex")(
         qkv.data_ptr(), qkv.stride(0), pages.data_ptr(), pages.shape[0], block_table.data_ptr(),
         block_table.shape[1], req_indptr.data_ptr(), kv_before.data_ptr(), _ptr(tile_req), _ptr(tile_row), tiles,
         out.data_ptr(), out.stride(0), tokens, nh, nkv, d, page_size, int(window or 0), float(scale),
         1 if rows16 else 0, splits,
-        _ptr(ws), ws.numel() * 4 if ws is not None else 0, _ptr(arrivals), 1 if late_wait else 0, _stream())
+        _ptr(ws), ws.numel() * 4 if ws is not None else 0, _ptr(arrivals), 1 if late_wait else 0,
+        float(softcap or 0.0), 1 if sink else 0, _ptr(gate), gate.stride(0) if gate is not None else 0, _stream())
     _check(code, "attention_mma", 2 if splits > 1 and arrivals is None else 1)
 
 

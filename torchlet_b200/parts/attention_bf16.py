@@ -117,16 +117,21 @@ def _plan(ctx, group_size: int, rows_per_tile: int = ROWS):
     return plan
 
 
-def forward(mixer, ctx, qkv, cache, out) -> bool:
+def forward(mixer, ctx, qkv, cache, out, gate=None) -> bool:
+    """``qkv``: rows whose first ``nh * d`` entries are the (encoded) queries; keys and values are in
+    the cache pages.  A mixer with a score cap (``mixer.softcap``), a sink (``mixer.sink``) or an output
+    ``gate`` runs its prompt portions, too, on the mma.sync kernel, which takes them as arguments."""
     d, nh, nkv = mixer.head_dim, mixer.num_heads, mixer.num_kv_heads
     group = nh // nkv
     if d not in (64, 128) or group > 16 or qkv.stride(0) % 8:
         return False
+    softcap, sink = getattr(mixer, "softcap", None), bool(getattr(mixer, "sink", False))
+    extras = bool(softcap) or sink or gate is not None
     # prompt portions: the tcgen05 kernel where it takes the page size, else the mma.sync kernel
-    use_tc = (not ctx.decode_only) and ops.attention_tc_supported(d, group, cache.page_size)
+    use_tc = (not ctx.decode_only) and not extras and ops.attention_tc_supported(d, group, cache.page_size)
     plan = _plan(ctx, group, ops.attention_tc_rows(group) if use_tc else ROWS)
     common = dict(out=out, tokens=ctx.num_tokens, nh=nh, nkv=nkv, d=d, page_size=cache.page_size,
-                  window=mixer.window, scale=mixer.scale)
+                  window=mixer.window, scale=mixer.scale, softcap=softcap, sink=sink, gate=gate)
     # A mixed step: the prompt portions first (few CTAs that walk long contexts), the decoding
     # requests' kernel right behind it on the SMs it leaves idle; the two touch different rows.
     merge_portions, beside = None, False

@@ -115,8 +115,13 @@ class GatedAttentionMixer(Mixer):
             positions.dims if positions is not None else 0, self.v_offset, write_kv=cache.writable)
         out = ctx.buffer("gated_attention.out", (tokens, self.q_size), ctx.dtype)
         gate = proj[:, self.gate_offset:] if self.gate else None
-        ops.attention_generic(q, q.stride(0), cache.pages, cache.block_table, ctx.token_req, ctx.positions, out, tokens,
-                              self.num_heads, self.num_kv_heads, self.head_dim, cache.page_size, self.window, self.scale,
-                              softcap=self.softcap, sink=self.sink, gate=gate)
+        from . import attention_bf16
+
+        # bfloat16 heads of 64 or 128: the tensor-core kernel (tiles of 16 packed rows for single tokens, of 64
+        # for prompt portions); else, and in float32, one warp per (token, head)
+        if not (ctx.dtype == torch.bfloat16 and attention_bf16.forward(self, ctx, q, cache, out, gate=gate)):
+            ops.attention_generic(q, q.stride(0), cache.pages, cache.block_table, ctx.token_req, ctx.positions, out, tokens,
+                                  self.num_heads, self.num_kv_heads, self.head_dim, cache.page_size, self.window, self.scale,
+                                  softcap=self.softcap, sink=self.sink, gate=gate)
         if not self.o_proj.accumulate_later(ctx, out, acc):
             self.o_proj.forward(out, acc, accumulate=True)

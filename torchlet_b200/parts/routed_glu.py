@@ -8,7 +8,11 @@ weight multiplies the expert's INPUT (``weight_on`` "input": out = sum_j expert_
 ("output": out = sum_j w_j expert_j(x)).
 
 Routing, the expert-sorted order and the products are planned and run on the device (csrc/moe.cu):
-nothing is read back, so steps of single tokens are captured like any other part's.
+nothing is read back, so steps of single tokens are captured like any other part's.  In bfloat16 the
+two products run on the tcgen05 tensor cores as grouped products over 128-row tiles that each belong
+to one expert (the persistent kernel of csrc/gemm_tc.cu with a plan), the first with the gated
+activation in its epilogue over gate and up rows interleaved by 16; in float32, and at sizes that
+kernel does not take, on CUDA cores in tiles of 64 rows.
 
 Parameters: ``hidden_size``, ``intermediate_size``, ``limit``, ``alpha``, ``num_experts``, ``top_k``,
 ``score``, ``renormalize``, ``weight_on``.  Tensors below the prefix: router [E, hidden];
@@ -46,6 +50,7 @@ class RoutedClampedGLU(FeedForward):
         if self.num_experts > 256:
             raise ValueError("the router kernel takes up to 256 experts")
         self.router = self.gate_up = self.down = None
+        self.tensor_cores = False
 
     @classmethod
     def expected_tensors(cls, spec: PartSpec, prefix: str) -> list[TensorSpec]:
@@ -61,8 +66,14 @@ class RoutedClampedGLU(FeedForward):
     def load(self, tensors: dict, prefix: str, device, dtype) -> None:
         E = self.num_experts
         self.router = tensors[prefix + "router"].to(device=device, dtype=torch.float32).contiguous()
-        # per expert [gate; up] stacked, [E, 2 ff, hidden], and [E, hidden, ff]
-        self.gate_up = torch.stack([torch.cat([tensors[f"{prefix}e{e}.gate"], tensors[f"{prefix}e{e}.up"]], dim=0)
+        from . import swiglu_bf16
+
+        # per expert [gate; up] stacked, [E, 2 ff, hidden], and [E, hidden, ff]; for the tensor-core product the
+        # gate and up rows of an expert are interleaved by 16 instead, as the gated epilogue reads them
+        self.tensor_cores = (dtype == torch.bfloat16 and swiglu_bf16.usable(self.hidden_size, self.intermediate_size)
+                             and self.intermediate_size % 8 == 0)
+        join = swiglu_bf16.interleave if self.tensor_cores else (lambda gate, up: torch.cat([gate, up], dim=0))
+        self.gate_up = torch.stack([join(tensors[f"{prefix}e{e}.gate"], tensors[f"{prefix}e{e}.up"])
                                     for e in range(E)]).to(device=device, dtype=dtype).contiguous()
         self.down = torch.stack([tensors[f"{prefix}e{e}.down"] for e in range(E)]).to(device=device, dtype=dtype).contiguous()
 
@@ -75,7 +86,7 @@ class RoutedClampedGLU(FeedForward):
 
     def forward(self, ctx, x, acc) -> None:
         tokens, top, E = x.shape[0], self.top_k, self.num_experts
-        tile = ops.moe_tile_rows()
+        tile = ops.GROUPED_TILE_ROWS if self.tensor_cores else ops.moe_tile_rows()
         tiles, rows = self._rows(tokens, tile)
         # scratch sized once for the largest step, so that its addresses never change
         most_tiles, most_rows = self._rows(max(ctx.token_capacity, tokens), tile)
@@ -90,6 +101,10 @@ class RoutedClampedGLU(FeedForward):
         ops.moe_route(x, self.router, choice, weight, self.score == "softmax", self.renormalize)
         ops.moe_plan(choice, position, plan, E, tile)
         ops.moe_scatter(x, position, weight, sorted_x, top, weighted=on_input)
-        ops.moe_gemm_simt(sorted_x, self.gate_up, act, plan, glu=True, limit=self.limit, alpha=self.alpha)
-        ops.moe_gemm_simt(act, self.down, y, plan)
+        if self.tensor_cores:
+            ops.gemm_tc_grouped(sorted_x, self.gate_up, act, plan, glu=True, limit=self.limit, alpha=self.alpha)
+            ops.gemm_tc_grouped(act, self.down, y, plan)
+        else:
+            ops.moe_gemm_simt(sorted_x, self.gate_up, act, plan, glu=True, limit=self.limit, alpha=self.alpha)
+            ops.moe_gemm_simt(act, self.down, y, plan)
         ops.moe_combine(y, position, weight, acc, top, weighted=not on_input)

@@ -10,10 +10,10 @@
 //
 // Three kernels:
 //   decay   one block per (8 tokens, 128 channels): a of every key channel;
-//   scan    one block per (request, head): the columns of S are independent of one another; four
-//           lanes share a column, each keeps a quarter of it in registers, and the block walks the
-//           request's tokens of this step in order; q, k, a, v of a few tokens at a time are staged in
-//           shared memory (two stages, asynchronous copies).  The state row of the request's slot
+//   scan    one block per (request, head, 32 value channels): the columns of S are independent of one
+//           another; four lanes share a column, each keeps a quarter of it in registers, and the block
+//           walks the request's tokens of this step in order; q, k, a, v of a few tokens at a time are
+//           staged in shared memory (four stages, asynchronous copies).  The state row of the request's slot
 //           is read at the start and written back at the end, so a prompt cut into portions, or
 //           decoded token by token, runs the same additions in the same order as the whole prompt;
 //   finish  one warp per (token, head): o / rms(o) * weight * silu(g) in the compute type (the
@@ -78,27 +78,33 @@ template <int N> __device__ __forceinline__ void copies_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-// One block per (request, head), KS * (vdim rounded up to 8) threads.  Four lanes share a column of
+// One block per (request, head, COLS value channels), KS * COLS threads.  Four lanes share a column of
 // S (value channel j): lane part p keeps the key channels i with (i / 4) % 4 == p, DK / 4 of them
 // (DK: the key size rounded up to 16, 32, 64, 128 or 256), and the sum over i of a token's S^T q meets
-// by two shuffles.  Every warp reads the same staged q, k, a of CHUNK tokens, two stages deep: while
-// the block walks one chunk, the next is on its way.
+// by two shuffles.  Every warp reads the same staged q, k, a of CHUNK tokens, STAGES stages deep: while
+// the block walks one chunk, the next three are on their way (a chunk's copies take longer than its
+// arithmetic).  A token costs a block 3 DK / 4 shared-memory reads of 16 bytes a warp, which is what bounds
+// a block of many warps; hence few columns a block, and more blocks.
 constexpr int KS = 4;
+constexpr int COLS = 32;
+constexpr int STAGES = 4;
 
 template <int DK, bool VEC>
-__global__ void __launch_bounds__(1024)
+__global__ void __launch_bounds__(KS * COLS)
 gla_scan_kernel(const float* __restrict__ proj, int proj_stride, const float* __restrict__ decay,
                 const int* __restrict__ req_indptr, const int* __restrict__ slots, float* __restrict__ state,
-                float* __restrict__ out, int heads, int dim, int vdim, int vpad, int max_slots, float qscale) {
+                float* __restrict__ out, int heads, int dim, int vdim, int max_slots, float qscale) {
   tl::pdl_launch_dependents();
   tl::pdl_wait();
   constexpr int PER = DK / KS;
   constexpr int CHUNK = DK <= 64 ? 8 : (DK <= 128 ? 4 : 2);
-  extern __shared__ __align__(16) float stage[];  // [2][CHUNK][3 DK + vpad]: q, k, a, v
-  const int row = 3 * DK + vpad;
-  const int NT = blockDim.x;
+  __shared__ __align__(16) float stage[STAGES * CHUNK * (3 * DK + COLS)];  // [STAGES][CHUNK]: q, k, a, v
+  constexpr int row = 3 * DK + COLS;
+  constexpr int NT = KS * COLS;
   const int req = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
-  const int part = tid % KS, col = tid / KS;
+  const int col0 = blockIdx.z * COLS;  // this block's value channels: col0 .. col0 + COLS
+  const int cols_here = vdim - col0 < COLS ? vdim - col0 : COLS;
+  const int part = tid % KS, col = col0 + tid / KS;
   const bool on = col < vdim;
   const int hd = heads * dim, hv = heads * vdim;
   const int first = req_indptr[req], last = req_indptr[req + 1];
@@ -110,13 +116,13 @@ gla_scan_kernel(const float* __restrict__ proj, int proj_stride, const float* __
     return;
   }
   // entries past dim (and past vdim) stay zero in both stages
-  for (int e = tid; e < 2 * CHUNK * row; e += NT) stage[e] = 0.f;
+  for (int e = tid; e < STAGES * CHUNK * row; e += NT) stage[e] = 0.f;
   __syncthreads();
   auto fetch = [&](int base, int buf) {
     const int count = last - base < CHUNK ? last - base : CHUNK;
     float* dst = stage + (size_t)buf * CHUNK * row;
     if (VEC) {
-      const int qd = dim >> 2, qv = vdim >> 2, per_token = 3 * qd + qv;
+      const int qd = dim >> 2, qv = cols_here >> 2, per_token = 3 * qd + qv;
       for (int e = tid; e < count * per_token; e += NT) {
         const int tt = e / per_token, rest = e - tt * per_token;
         const int t = base + tt;
@@ -132,13 +138,13 @@ gla_scan_kernel(const float* __restrict__ proj, int proj_stride, const float* __
           to = dst + tt * row + 2 * DK + 4 * q4;
         } else {
           const int q4 = rest - 3 * qd;
-          src = proj + (size_t)t * proj_stride + 2 * hd + h * vdim + 4 * q4;
+          src = proj + (size_t)t * proj_stride + 2 * hd + h * vdim + col0 + 4 * q4;
           to = dst + tt * row + 3 * DK + 4 * q4;
         }
         copy16(to, src);
       }
     } else {
-      const int per_token = 3 * dim + vdim;
+      const int per_token = 3 * dim + cols_here;
       for (int e = tid; e < count * per_token; e += NT) {
         const int tt = e / per_token, rest = e - tt * per_token;
         const int t = base + tt;
@@ -154,7 +160,7 @@ gla_scan_kernel(const float* __restrict__ proj, int proj_stride, const float* __
           to = dst + tt * row + 2 * DK + i;
         } else {
           const int i = rest - 3 * dim;
-          src = proj + (size_t)t * proj_stride + 2 * hd + h * vdim + i;
+          src = proj + (size_t)t * proj_stride + 2 * hd + h * vdim + col0 + i;
           to = dst + tt * row + 3 * DK + i;
         }
         copy4(to, src);
@@ -162,7 +168,10 @@ gla_scan_kernel(const float* __restrict__ proj, int proj_stride, const float* __
     }
     copies_commit();
   };
-  if (first < last) fetch(first, 0);
+  for (int s = 0; s < STAGES - 1; ++s) {  // always STAGES - 1 groups in flight (some of them empty)
+    if (first + s * CHUNK < last) fetch(first + s * CHUNK, s);
+    else copies_commit();
+  }
 
   // this lane's key channels: i = 4 (n / 4 * KS + part) + n % 4
   float* mine = state + ((size_t)slot * heads + h) * dim * vdim;
@@ -174,14 +183,12 @@ gla_scan_kernel(const float* __restrict__ proj, int proj_stride, const float* __
   }
 
   int buf = 0;
-  for (int base = first; base < last; base += CHUNK, buf ^= 1) {
+  for (int base = first; base < last; base += CHUNK, buf = (buf + 1) % STAGES) {
     const int count = last - base < CHUNK ? last - base : CHUNK;
-    if (base + CHUNK < last) {
-      fetch(base + CHUNK, buf ^ 1);
-      copies_wait<1>();
-    } else {
-      copies_wait<0>();
-    }
+    // the stage that the chunk before this one used is free (the barrier at the end of its walk)
+    if (base + (STAGES - 1) * CHUNK < last) fetch(base + (STAGES - 1) * CHUNK, (buf + STAGES - 1) % STAGES);
+    else copies_commit();
+    copies_wait<STAGES - 1>();  // all but the newest STAGES - 1 groups: this chunk has landed
     __syncthreads();
     const float* chunk = stage + (size_t)buf * CHUNK * row;
     for (int tt = 0; tt < count; ++tt) {
@@ -189,7 +196,7 @@ gla_scan_kernel(const float* __restrict__ proj, int proj_stride, const float* __
       const float4* q4 = reinterpret_cast<const float4*>(tok);
       const float4* k4 = reinterpret_cast<const float4*>(tok + DK);
       const float4* a4 = reinterpret_cast<const float4*>(tok + 2 * DK);
-      const float v = tok[3 * DK + (on ? col : 0)];
+      const float v = tok[3 * DK + (on ? col - col0 : 0)];
       float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
       for (int n = 0; n < PER / 4; ++n) {
@@ -271,21 +278,18 @@ int tl_gla_scan(const float* proj, int proj_stride, const float* decay, const in
                 cudaStream_t stream) {
   if (requests <= 0) return 0;
   if (dim <= 0 || dim > 256 || vdim <= 0 || vdim > 256 || heads > 65535) return TL_ERR_UNSUPPORTED;
-  dim3 grid(requests, heads);
-  const int vpad = (vdim + 7) & ~7;
-  const int threads = KS * vpad;
+  dim3 grid(requests, heads, (vdim + COLS - 1) / COLS);
+  const int threads = KS * COLS;
   const bool vec = dim % 4 == 0 && vdim % 4 == 0 && proj_stride % 4 == 0 && (heads * dim) % 4 == 0 &&
                    (reinterpret_cast<uintptr_t>(proj) & 15) == 0 && (reinterpret_cast<uintptr_t>(decay) & 15) == 0;
 #define TL_SCAN(DK)                                                                                                  \
   {                                                                                                                  \
-    constexpr int CHUNK = DK <= 64 ? 8 : (DK <= 128 ? 4 : 2);                                                        \
-    const size_t smem = (size_t)2 * CHUNK * (3 * DK + vpad) * sizeof(float);                                        \
     if (vec)                                                                                                         \
-      tl::launch_kernel(gla_scan_kernel<DK, true>, grid, threads, smem, stream, proj, proj_stride, decay, req_indptr, \
-                        slots, state, out, heads, dim, vdim, vpad, max_slots, qscale);                               \
+      tl::launch_kernel(gla_scan_kernel<DK, true>, grid, threads, 0, stream, proj, proj_stride, decay, req_indptr,   \
+                        slots, state, out, heads, dim, vdim, max_slots, qscale);                                     \
     else                                                                                                             \
-      tl::launch_kernel(gla_scan_kernel<DK, false>, grid, threads, smem, stream, proj, proj_stride, decay,           \
-                        req_indptr, slots, state, out, heads, dim, vdim, vpad, max_slots, qscale);                   \
+      tl::launch_kernel(gla_scan_kernel<DK, false>, grid, threads, 0, stream, proj, proj_stride, decay,              \
+                        req_indptr, slots, state, out, heads, dim, vdim, max_slots, qscale);                         \
   }
   if (dim <= 16) TL_SCAN(16)
   else if (dim <= 32) TL_SCAN(32)

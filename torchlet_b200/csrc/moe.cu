@@ -26,9 +26,12 @@ namespace {
 
 using namespace tl;
 
-constexpr int ROUTE_WARPS = 4;
+constexpr int ROUTE_WARPS = 8;
 constexpr int MAX_EXPERTS = 256;
 
+// One block per token.  The token's row is staged in shared memory as floats; warp w takes the
+// experts w, w + 8, ...: each lane sums its 32nd of the row in four independent chains (k = lane,
+// lane + 32, ... in turn), so a logit's order of additions depends on the width alone.
 template <typename T>
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ router, int* __restrict__ choice,
@@ -36,29 +39,40 @@ moe_route_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ rou
                  int renormalize) {
   tl::pdl_launch_dependents();
   tl::pdl_wait();
-  __shared__ float score[ROUTE_WARPS][MAX_EXPERTS];
+  extern __shared__ float xrow[];  // hidden floats
+  __shared__ float all_scores[MAX_EXPERTS];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * ROUTE_WARPS + warp;
-  if (t >= tokens) return;
+  const int t = blockIdx.x;
   const T* row = x + (size_t)t * ldx;
-  for (int e = 0; e < experts; ++e) {
+  for (int k = threadIdx.x; k < hidden; k += ROUTE_WARPS * 32) xrow[k] = to_float(row[k]);
+  __syncthreads();
+  for (int e = warp; e < experts; e += ROUTE_WARPS) {
     const float* w = router + (size_t)e * hidden;
-    float part = 0.f;
-    for (int k = lane; k < hidden; k += 32) part = fmaf(to_float(row[k]), w[k], part);
-    part = warp_sum(part);
-    if (lane == 0) score[warp][e] = part;
+    float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
+    int k = lane;
+    for (; k + 96 < hidden; k += 128) {
+      p0 = fmaf(xrow[k], w[k], p0);
+      p1 = fmaf(xrow[k + 32], w[k + 32], p1);
+      p2 = fmaf(xrow[k + 64], w[k + 64], p2);
+      p3 = fmaf(xrow[k + 96], w[k + 96], p3);
+    }
+    for (; k < hidden; k += 32) p0 = fmaf(xrow[k], w[k], p0);
+    const float part = warp_sum((p0 + p1) + (p2 + p3));
+    if (lane == 0) all_scores[e] = part;
   }
-  __syncwarp();
+  __syncthreads();
+  if (warp != 0) return;
+  float* score = all_scores;  // the first warp alone goes on: scores, the choice, the weights
   if (softmax_scores) {
     float m = -INFINITY;
-    for (int e = lane; e < experts; e += 32) m = fmaxf(m, score[warp][e]);
+    for (int e = lane; e < experts; e += 32) m = fmaxf(m, score[e]);
     m = warp_max(m);
     float l = 0.f;
-    for (int e = lane; e < experts; e += 32) l += expf(score[warp][e] - m);
+    for (int e = lane; e < experts; e += 32) l += expf(score[e] - m);
     l = warp_sum(l);
-    for (int e = lane; e < experts; e += 32) score[warp][e] = expf(score[warp][e] - m) / l;
+    for (int e = lane; e < experts; e += 32) score[e] = expf(score[e] - m) / l;
   } else {
-    for (int e = lane; e < experts; e += 32) score[warp][e] = 1.f / (1.f + expf(-score[warp][e]));
+    for (int e = lane; e < experts; e += 32) score[e] = 1.f / (1.f + expf(-score[e]));
   }
   __syncwarp();
   float total = 0.f;
@@ -66,7 +80,7 @@ moe_route_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ rou
     float best = -INFINITY;
     int at = experts;
     for (int e = lane; e < experts; e += 32) {
-      const float s = score[warp][e];
+      const float s = score[e];
       if (s > best) { best = s; at = e; }  // ascending e: the lower index keeps a tie
     }
 #pragma unroll
@@ -80,7 +94,7 @@ moe_route_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ rou
     if (lane == 0) {
       choice[(size_t)t * top + j] = at;
       weight[(size_t)t * top + j] = best;
-      score[warp][at] = -INFINITY;
+      score[at] = -INFINITY;
     }
     __syncwarp();
   }
@@ -246,12 +260,14 @@ int tl_moe_route(const void* x, int ldx, int dtype, const float* router, int* ch
                  int hidden, int experts, int top, int softmax_scores, int renormalize, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (experts <= 0 || experts > MAX_EXPERTS || top <= 0 || top > experts) return TL_ERR_UNSUPPORTED;
-  const unsigned blocks = (tokens + ROUTE_WARPS - 1) / ROUTE_WARPS;
+  const unsigned blocks = tokens;
+  const size_t smem = (size_t)hidden * sizeof(float);
+  if (smem > 48 * 1024) return TL_ERR_UNSUPPORTED;
   if (dtype == TL_DTYPE_F32)
-    tl::launch_kernel(moe_route_kernel<float>, blocks, ROUTE_WARPS * 32, 0, stream, (const float*)x, ldx, router, choice,
+    tl::launch_kernel(moe_route_kernel<float>, blocks, ROUTE_WARPS * 32, smem, stream, (const float*)x, ldx, router, choice,
                       weight, tokens, hidden, experts, top, softmax_scores, renormalize);
   else
-    tl::launch_kernel(moe_route_kernel<__nv_bfloat16>, blocks, ROUTE_WARPS * 32, 0, stream, (const __nv_bfloat16*)x,
+    tl::launch_kernel(moe_route_kernel<__nv_bfloat16>, blocks, ROUTE_WARPS * 32, smem, stream, (const __nv_bfloat16*)x,
                       ldx, router, choice, weight, tokens, hidden, experts, top, softmax_scores, renormalize);
   return TL_LAUNCH_CHECK();
 }

@@ -75,12 +75,12 @@ __global__ void scaled_add_kernel(float4* __restrict__ acc, const float4* __rest
 // additions depends only on the width.
 template <int NT>
 __global__ void __launch_bounds__(NT)
-rms_scaled_add_kernel(float* __restrict__ acc, const float* __restrict__ y, const float* __restrict__ w, float m,
-                      float eps, int hidden) {
+rms_scaled_add_kernel(float* __restrict__ acc, float* __restrict__ y, const float* __restrict__ w, float m,
+                      float eps, int hidden, int clear) {
   tl::pdl_launch_dependents();
   tl::pdl_wait();
   __shared__ float scratch[32];
-  const float* row = y + (size_t)blockIdx.x * hidden;
+  float* row = y + (size_t)blockIdx.x * hidden;
   float* out = acc + (size_t)blockIdx.x * hidden;
   float ss = 0.f;
   for (int j = threadIdx.x; j < hidden; j += NT) {
@@ -89,7 +89,10 @@ rms_scaled_add_kernel(float* __restrict__ acc, const float* __restrict__ y, cons
   }
   ss = block_sum<NT>(ss, scratch);
   const float inv = rsqrtf(ss / (float)hidden + eps);
-  for (int j = threadIdx.x; j < hidden; j += NT) out[j] = fmaf(m, row[j] * inv * w[j], out[j]);
+  for (int j = threadIdx.x; j < hidden; j += NT) {
+    out[j] = fmaf(m, row[j] * inv * w[j], out[j]);
+    if (clear) row[j] = 0.f;  // the side stream is left zeroed for the next sub-layer to add into
+  }
 }
 
 __device__ __forceinline__ float gelu_tanh(float z) {
@@ -164,13 +167,13 @@ int tl_scaled_add(float* acc, const float* delta, float m, void* cast, long long
   return TL_LAUNCH_CHECK();
 }
 
-int tl_rms_scaled_add(float* acc, const float* y, const float* w, float m, float eps, int rows, int hidden,
+int tl_rms_scaled_add(float* acc, float* y, const float* w, float m, float eps, int rows, int hidden, int clear,
                       cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (hidden <= 1024)
-    tl::launch_kernel(rms_scaled_add_kernel<128>, rows, 128, 0, stream, acc, y, w, m, eps, hidden);
+    tl::launch_kernel(rms_scaled_add_kernel<128>, rows, 128, 0, stream, acc, y, w, m, eps, hidden, clear);
   else
-    tl::launch_kernel(rms_scaled_add_kernel<512>, rows, 512, 0, stream, acc, y, w, m, eps, hidden);
+    tl::launch_kernel(rms_scaled_add_kernel<512>, rows, 512, 0, stream, acc, y, w, m, eps, hidden, clear);
   return TL_LAUNCH_CHECK();
 }
 

@@ -100,7 +100,7 @@ _SIGNATURES = {
         "tl_fill_zero": [c_void_p, c_longlong, c_void_p],
         "tl_scale": [c_void_p, c_float, c_longlong, c_void_p],
         "tl_scaled_add": [c_void_p, c_void_p, c_float, c_void_p, c_longlong, c_void_p],
-        "tl_rms_scaled_add": [c_void_p, c_void_p, c_void_p, c_float, c_float, c_int, c_int, c_void_p],
+        "tl_rms_scaled_add": [c_void_p, c_void_p, c_void_p, c_float, c_float, c_int, c_int, c_int, c_void_p],
         "tl_gated_token_embed": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
         "tl_clamped_glu": [c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p],
         "tl_stream_ops_debug_error": [c_void_p],
@@ -348,14 +348,15 @@ def scaled_add(acc: torch.Tensor, delta: torch.Tensor, m: float, cast: torch.Ten
     _check(code, "scaled_add")
 
 
-def rms_scaled_add(acc: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, m: float, eps: float) -> None:
-    """acc[r] += m * y[r] / sqrt(mean(y[r]^2) + eps) * weight;  all float32."""
+def rms_scaled_add(acc: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, m: float, eps: float,
+                   clear: bool = False) -> None:
+    """acc[r] += m * y[r] / sqrt(mean(y[r]^2) + eps) * weight;  all float32.  ``clear``: y is left zeroed."""
     _need_cuda(acc, y, weight)
     rows, hidden = acc.shape
     assert acc.dtype == y.dtype == weight.dtype == torch.float32 and y.shape == acc.shape
     assert acc.is_contiguous() and y.is_contiguous() and weight.numel() == hidden
     code = _fn("stream_ops", "tl_rms_scaled_add")(acc.data_ptr(), y.data_ptr(), weight.data_ptr(), float(m),
-                                                  float(eps), rows, hidden, _stream())
+                                                  float(eps), rows, hidden, 1 if clear else 0, _stream())
     _check(code, "rms_scaled_add")
 
 

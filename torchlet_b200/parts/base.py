@@ -92,10 +92,10 @@ class Norm(Part):
         dtype; ``out`` or a buffer called ``name`` receives them."""
         raise NotImplementedError
 
-    def add_normed(self, ctx, y, acc, m: float = 1.0) -> None:
+    def add_normed(self, ctx, y, acc, m: float = 1.0, clear: bool = False) -> None:
         """acc += m * norm(y) in float32, for a norm that stands BEHIND a sub-layer (``y`` is the
-        float32 side stream the sub-layer added its output into).  Only norms that a block
-        arrangement uses in that place implement it."""
+        float32 side stream the sub-layer added its output into; ``clear``: and leave y zeroed).
+        Only norms that a block arrangement uses in that place implement it."""
         raise NotImplementedError(f"the norm {self.kind!r} cannot stand behind a sub-layer")
 
 

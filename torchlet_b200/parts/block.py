@@ -55,7 +55,8 @@ class SandwichBlock(Block):
     """x += post(mixer(pre(x))); then, if the layer has a feed-forward, x += post'(ff(pre'(x))).
     Each sub-layer adds its output into a zeroed float32 stream of its own, the norm behind it
     reads that stream and adds the normed rows into the residual stream (``Norm.add_normed``), so
-    the sub-layer's output, its norm and the residual sum are all float32."""
+    the sub-layer's output, its norm and the residual sum are all float32.  That norm's kernel also
+    leaves the side stream zeroed again, so it is cleared by a kernel of its own once a step only."""
 
     norm_roles = ("mixer_norm", "mixer_post_norm")
 
@@ -69,11 +70,12 @@ class SandwichBlock(Block):
     def forward(self, ctx, acc, cache) -> None:
         side = ctx.buffer("sandwich.side", tuple(acc.shape), acc.dtype)
         x = self.norms["mixer_norm"].apply(ctx, acc)
-        ops.fill_zero(side)
+        if ctx.plans.get("sandwich.side.clean") is not side:  # the first sandwich block of the step
+            ops.fill_zero(side)
+            ctx.plans["sandwich.side.clean"] = side
         self.mixer.forward(ctx, x, side, cache)
-        self.norms["mixer_post_norm"].add_normed(ctx, side, acc)
+        self.norms["mixer_post_norm"].add_normed(ctx, side, acc, clear=True)
         if self.feed_forward is not None:
             x = self.norms["feed_forward_norm"].apply(ctx, acc)
-            ops.fill_zero(side)
             self.feed_forward.forward(ctx, x, side)
-            self.norms["feed_forward_post_norm"].add_normed(ctx, side, acc)
+            self.norms["feed_forward_post_norm"].add_normed(ctx, side, acc, clear=True)

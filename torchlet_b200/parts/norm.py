@@ -58,9 +58,9 @@ class RMSNorm(Norm):
         ops.rms_norm(acc, self.weight, self.eps, out, rows, self.groups)
         return out
 
-    def add_normed(self, ctx, y, acc, m: float = 1.0) -> None:
+    def add_normed(self, ctx, y, acc, m: float = 1.0, clear: bool = False) -> None:
         """acc += m * norm(y): both float32 ``[T, size]``; ``y`` is a side stream a sub-layer added its
-        output into."""
+        output into.  ``clear``: y is zeroed in the same pass, ready for the next sub-layer."""
         if self.groups != 1:
             raise ValueError("the norm of a sub-layer's output is not built for grouped norms")
         pending = ctx.take_pending(y)
@@ -68,4 +68,4 @@ class RMSNorm(Norm):
             ops.finish_accum_norm(pending.partials, pending.splits, pending.bias, y)
         else:
             ctx.flush_pending()
-        ops.rms_scaled_add(acc, y, self.weight, m, self.eps)
+        ops.rms_scaled_add(acc, y, self.weight, m, self.eps, clear)

@@ -385,8 +385,21 @@ gemm_tc_swapped_kernel(const __grid_constant__ CUtensorMap map_row, const __grid
 // role of the CTA asks with the same arguments, so all of them skip the same tiles.
 __device__ __forceinline__ int tile_group(const Params& p, int tile) {
   if (!p.plan) return 0;
-  const int row_tile = tile % p.row_tiles;
+  const int row_tile = tile / (p.num_tiles / p.row_tiles);
   return row_tile < p.plan[0] ? p.plan[1 + row_tile] : -1;
+}
+// Row and column tile of a tile index.  One group: row tiles fastest, so that the CTAs that run together share
+// weight tiles.  With a plan: column tiles fastest, so that the CTAs that run together work on the few row tiles
+// of one or two groups and need those groups' weights only.
+__device__ __forceinline__ void tile_coords(const Params& p, int tile, int* row_tile, int* col_tile) {
+  if (p.plan) {
+    const int col_tiles = p.num_tiles / p.row_tiles;
+    *row_tile = tile / col_tiles;
+    *col_tile = tile - *row_tile * col_tiles;
+  } else {
+    *row_tile = tile % p.row_tiles;
+    *col_tile = tile / p.row_tiles;
+  }
 }
 
 // Normal orientation, persistent: one CTA per SM walks over output tiles (row tiles
@@ -444,7 +457,9 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_row, const __g
       for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
         const int group = tile_group(p, tile);
         if (group < 0) continue;
-        const int row0 = (tile % p.row_tiles) * BLOCK_P, col0 = (tile / p.row_tiles) * p.block_q;
+        int row_tile, col_tile;
+        tile_coords(p, tile, &row_tile, &col_tile);
+        const int row0 = row_tile * BLOCK_P, col0 = col_tile * p.block_q;
         const int wrow0 = group * p.group_rows + col0;
         for (int kb = 0; kb < num_kb; ++kb) {
           mbar_wait(&empty[s], phase ^ 1, abort_flag, &g_error_word, 1);
@@ -503,7 +518,9 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_row, const __g
     for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
       if (tile_group(p, tile) < 0) continue;
       const int a = local & 1;
-      const int row0 = (tile % p.row_tiles) * BLOCK_P, col0 = (tile / p.row_tiles) * p.block_q;
+      int row_tile, col_tile;
+      tile_coords(p, tile, &row_tile, &col_tile);
+      const int row0 = row_tile * BLOCK_P, col0 = col_tile * p.block_q;
       mbar_wait(&tmem_full[a], (local >> 1) & 1, abort_flag, &g_error_word, 3);
       fence_after_sync();
       const int row = row0 + quarter * 32 + lane;

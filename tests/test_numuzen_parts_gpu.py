@@ -199,8 +199,9 @@ def test_attention_with_cap_sink_and_window_on_designed_keys(dtype, window, page
 @pytest.mark.parametrize("softcap,sink,gated", [(20.0, True, True), (None, True, False), (30.0, False, False)])
 def test_tensor_core_attention_with_cap_sink_gate_equals_the_plain_kernel(d, H, G, window, page_size, softcap, sink, gated):
     """The mma.sync kernel (64-row tiles for a prompt portion, 16-row tiles with 1, 3 and 20 key splits for a
-    single token, merged inside the kernel and by the second kernel) against the one-warp-a-row kernel on the
-    same pages, with two designed keys at the window's edge."""
+    single token, merged inside the kernel and by the second kernel) and the tcgen05 kernel (a prompt portion,
+    whole and with key splits) against the one-warp-a-row kernel on the same pages, with two designed keys at
+    the window's edge."""
     from torchlet_b200 import ops
 
     T, scale, g = 700, d ** -0.5, H // G
@@ -230,6 +231,19 @@ def test_tensor_core_attention_with_cap_sink_gate_equals_the_plain_kernel(d, H, 
     ops.attention_mma(qd, pages, table, indptr, before, torch.zeros_like(rows), rows, rows.numel(), got, T, H, G, d, page_size,
                       window, scale, rows16=False, softcap=softcap, sink=sink, gate=gate_view)
     close(got, want.float().cpu(), 2e-2, "prompt portion")
+    # the same on the tcgen05 kernel: whole, with the keys split over three CTAs, and with the merge deferred
+    if ops.attention_tc_supported(d, g, page_size):
+        per = ops.attention_tc_rows(g)
+        rows = torch.arange(0, T * g, per, dtype=torch.int32, device=DEV)
+        for splits, defer in ((1, False), (3, False), (2, True)):
+            got = torch.full((T, H * d), float("nan"), dtype=td, device=DEV)
+            merge = ops.attention_tc(qd, pages, table, indptr, before, torch.zeros_like(rows), rows, rows.numel(), got, H, G, d,
+                                     page_size, window, scale, splits=splits, token_req=zeros, defer_merge=defer,
+                                     softcap=softcap, sink=sink, gate=gate_view)
+            if defer:
+                merge()
+            close(got, want.float().cpu(), 2e-2, f"prompt portion on tcgen05, {splits} key splits")
+        ops.raise_on_wait_errors()
     # the last token alone, behind 699 cached ones
     indptr = torch.tensor([0, 1], dtype=torch.int32, device=DEV)
     before = torch.tensor([last], dtype=torch.int32, device=DEV)

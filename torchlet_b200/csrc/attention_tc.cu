@@ -74,7 +74,22 @@ struct Params {
   float* part_acc;  // splits > 1: [tokens * nh][splits][D] unnormalized outputs
   float* part_ml;   //             [tokens * nh][splits][2] reference max (log2 units) and sum
   float scale_log2;
+  // options: a score cap, s <- cap tanh(s / cap) (cap_inner = scale / cap, cap_outer = cap * log2(e); 0: off);
+  // a sink (one more in the softmax's denominator: a key of score 0 without a value); an output gate
+  // (float32 rows [tokens][>= nh D]: the output is multiplied by sigmoid(gate))
+  float cap_inner, cap_outer;
+  int sink;
+  const float* gate;
+  long long gate_stride;
 };
+
+// tanh by the special-function unit (tanh.approx: relative error 2^-11, which the cap's factor turns into a
+// score error of a few thousandths where scores are far from the cap, and the weights are rounded to bfloat16)
+__device__ __forceinline__ float fast_tanh(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
   const int bytes = valid ? 16 : 0;
@@ -397,6 +412,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
 #pragma unroll
       for (int c = 0; c < KEYS; c += 32) tmem_ld_32(tmem_s + c, reinterpret_cast<uint32_t(&)[32]>(v[c]));
       tmem_ld_wait();
+      if (p.cap_outer > 0.f) {  // capped scores: tanh(s scale / cap), scaled by cap log2(e) below
+#pragma unroll
+        for (int i = 0; i < KEYS; ++i) v[i] = __float_as_uint(fast_tanh(__uint_as_float(v[i]) * p.cap_inner));
+      }
+      const float mult = p.cap_outer > 0.f ? p.cap_outer : p.scale_log2;
       // A tile whose keys are all visible to every row of this warp needs no masking; rows beyond
       // the tile's last (zero queries, never stored) take whatever comes
       const bool visible = !row_valid || (key0 + KEYS - 1 <= pos && key0 >= lo);
@@ -418,7 +438,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
         m_c = max3(m_c, __uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
         m_d = max3(m_d, __uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
       }
-      const float m_tile = fmaxf(fmaxf(m_a, m_b), fmaxf(m_c, m_d)) * p.scale_log2;  // the scale is positive
+      const float m_tile = fmaxf(fmaxf(m_a, m_b), fmaxf(m_c, m_d)) * mult;  // the factor is positive
       // the reference max moves only when the row's max has grown past the threshold
       float factor = 1.f;
       bool rescale = false;
@@ -443,7 +463,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
       // P = exp2(S * scale - m_ref) as bfloat16 pairs over the first half of S's columns; row sum
       const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
       float sum_a = 0.f, sum_b = 0.f;
-      exp_and_store(v, p.scale_log2, neg_m, tmem_s, sum_a, sum_b);
+      exp_and_store(v, mult, neg_m, tmem_s, sum_a, sum_b);
       l_sum += sum_a + sum_b;
       tmem_st_wait();
       fence_before_sync();  // our tcgen05.ld/st of S, P and O are done
@@ -476,9 +496,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
     } else if (num_tiles > 0) {
       mbar_wait(&o_done[x], 0, abort_flag, &g_error_word, 9);
       fence_after_sync();
+      if (p.sink && m_ref != -INFINITY) l_sum += exp2f(-m_ref);  // the sink's share: a key of score 0
       const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
       __nv_bfloat16* dst = nullptr;
+      const float* gate = nullptr;
       if (row_valid) dst = p.out + (size_t)(tok0 + row / g) * p.out_stride + (size_t)(kvh * g + row % g) * D;
+      if (row_valid && p.gate) gate = p.gate + (size_t)(tok0 + row / g) * p.gate_stride + (size_t)(kvh * g + row % g) * D;
 #pragma unroll 1
       for (int c = 0; c < D; c += 32) {
         uint32_t o[32];
@@ -488,7 +511,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
           uint32_t packed[16];
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+            float a = __uint_as_float(o[i]) * inv, b = __uint_as_float(o[i + 1]) * inv;
+            if (gate) {
+              a *= 1.f / (1.f + __expf(-gate[c + i]));
+              b *= 1.f / (1.f + __expf(-gate[c + i + 1]));
+            }
+            __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
             packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
           }
 #pragma unroll
@@ -514,7 +542,8 @@ template <int D>
 __global__ void __launch_bounds__(128)
 attention_tc_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                           const int* __restrict__ token_req, const int* __restrict__ req_indptr,
-                          __nv_bfloat16* __restrict__ out, long long out_stride, int tokens, int nh, int splits) {
+                          __nv_bfloat16* __restrict__ out, long long out_stride, int tokens, int nh, int splits, int sink,
+                          const float* __restrict__ gate, long long gate_stride) {
   tl::pdl_launch_dependents();
   tl::pdl_wait();
   const int item = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -538,10 +567,16 @@ attention_tc_merge_kernel(const float* __restrict__ part_acc, const float* __res
 #pragma unroll
     for (int i = 0; i < PER; ++i) acc[i] = fmaf(src[i], f, acc[i]);
   }
+  if (sink && m_all != -INFINITY) total += exp2f(-m_all);  // the sink's share: a key of score 0
   const float inv = total > 0.f ? 1.f / total : 0.f;
   __nv_bfloat16* dst = out + (size_t)token * out_stride + (size_t)head * D + lane * PER;
+  const float* gate_row = gate ? gate + (size_t)token * gate_stride + (size_t)head * D + lane * PER : nullptr;
 #pragma unroll
-  for (int i = 0; i < PER; ++i) dst[i] = __float2bfloat16_rn(acc[i] * inv);
+  for (int i = 0; i < PER; ++i) {
+    float v = acc[i] * inv;
+    if (gate_row) v *= 1.f / (1.f + __expf(-gate_row[i]));
+    dst[i] = __float2bfloat16_rn(v);
+  }
 }
 
 // ------------------------------------------------------------------ host side
@@ -576,7 +611,8 @@ bool cached_map(CUtensorMap* out, const void* base, uint64_t rows, uint32_t cols
 template <int D>
 int launch_merge(const Params& p, const int* token_req, int tokens, cudaStream_t stream) {
   tl::launch_kernel(attention_tc_merge_kernel<D>, (tokens * p.nh + 3) / 4, 128, 0, stream, (const float*)p.part_acc,
-                    (const float*)p.part_ml, token_req, p.req_indptr, p.out, p.out_stride, tokens, p.nh, p.splits);
+                    (const float*)p.part_ml, token_req, p.req_indptr, p.out, p.out_stride, tokens, p.nh, p.splits, p.sink,
+                    p.gate, p.gate_stride);
   return TL_LAUNCH_CHECK();
 }
 
@@ -628,7 +664,8 @@ int tl_attention_tc(const void* q, long long q_stride, const void* pages, long l
                     const int* block_table, int table_width, const int* req_indptr, const int* kv_before,
                     const int* tile_req, const int* tile_row, int tiles, void* out, long long out_stride, int nh,
                     int nkv, int d, int page_size, int window, float scale, int splits, const int* token_req,
-                    int tokens, void* workspace, long long workspace_bytes, int defer_merge, cudaStream_t stream) {
+                    int tokens, void* workspace, long long workspace_bytes, int defer_merge, float softcap, int sink,
+                    const float* gate, long long gate_stride, cudaStream_t stream) {
   if (tiles <= 0) return 0;
   if (splits < 1 || splits > 64) return TL_ERR_UNSUPPORTED;
   if (splits > 1 && (!token_req || tokens <= 0 || !workspace ||
@@ -657,6 +694,11 @@ int tl_attention_tc(const void* q, long long q_stride, const void* pages, long l
   p.window = window;
   p.rows_per_tile = tl_attention_tc_rows(nh / nkv) / QTILES;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.cap_inner = softcap > 0.f ? scale / softcap : 0.f;
+  p.cap_outer = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
+  p.sink = sink;
+  p.gate = gate;
+  p.gate_stride = gate_stride;
   p.splits = splits;
   p.part_acc = (float*)workspace;
   p.part_ml = p.part_acc + (size_t)(splits > 1 ? tokens : 0) * nh * splits * d;
@@ -667,8 +709,8 @@ int tl_attention_tc(const void* q, long long q_stride, const void* pages, long l
 // The merge that a tl_attention_tc call with defer_merge left undone: same out, sizes, splits,
 // token_req and workspace as that call.
 int tl_attention_tc_merge(const int* req_indptr, void* out, long long out_stride, int nh, int d, int splits,
-                          const int* token_req, int tokens, void* workspace, long long workspace_bytes,
-                          cudaStream_t stream) {
+                          const int* token_req, int tokens, void* workspace, long long workspace_bytes, int sink,
+                          const float* gate, long long gate_stride, cudaStream_t stream) {
   if (splits <= 1 || tokens <= 0) return 0;
   if ((d != 64 && d != 128) || !token_req || !workspace || out_stride % 8 ||
       workspace_bytes < tl_attention_tc_workspace(tokens, nh, d, splits))
@@ -680,6 +722,9 @@ int tl_attention_tc_merge(const int* req_indptr, void* out, long long out_stride
   p.out_stride = out_stride;
   p.nh = nh;
   p.splits = splits;
+  p.sink = sink;
+  p.gate = gate;
+  p.gate_stride = gate_stride;
   p.part_acc = (float*)workspace;
   p.part_ml = p.part_acc + (size_t)tokens * nh * splits * d;
   return d == 128 ? launch_merge<128>(p, token_req, tokens, stream) : launch_merge<64>(p, token_req, tokens, stream);

@@ -82,9 +82,10 @@ _SIGNATURES = {
     "attention_tc": {
         "tl_attention_tc": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                             c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_float,
-                            c_int, c_void_p, c_int, c_void_p, c_longlong, c_int, c_void_p],
+                            c_int, c_void_p, c_int, c_void_p, c_longlong, c_int, c_float, c_int, c_void_p, c_longlong,
+                            c_void_p],
         "tl_attention_tc_merge": [c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_int, c_void_p,
-                                  c_longlong, c_void_p],
+                                  c_longlong, c_int, c_void_p, c_longlong, c_void_p],
         "tl_attention_tc_error": [],
         "tl_attention_tc_rows": [c_int],
     },
@@ -902,15 +903,18 @@ def attention_tc_supported(d: int, group: int, page_size: int) -> bool:
 
 
 def attention_tc(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile_row, tiles, out, nh, nkv, d,
-                 page_size, window, scale, splits: int = 1, token_req=None, defer_merge: bool = False):
+                 page_size, window, scale, splits: int = 1, token_req=None, defer_merge: bool = False,
+                 softcap=None, sink: bool = False, gate=None):
     """Prompt-portion attention on tcgen05 (csrc/attention_tc.cu): tiles of packed rows
     (``tile_row`` multiples of ``attention_tc_rows(nh // nkv)``) that cover every request of the
     step with more than one token.  ``splits`` > 1: that many CTAs share the key tiles of each
     (row tiles, KV head) and a second kernel merges them (``token_req``: each token's request).
     ``defer_merge``: that second kernel is not launched; the call returns a function that launches
     it (None when there is nothing to merge), so that the decode attention may run between the two.
-    The partial results have a workspace of their own."""
-    _need_cuda(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile_row, out, token_req)
+    The partial results have a workspace of their own.  ``softcap``, ``sink``, ``gate``: as in ``attention_mma``."""
+    _need_cuda(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile_row, out, token_req, gate)
+    assert gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1)
+    gate_stride = gate.stride(0) if gate is not None else 0
     assert qkv.dtype == pages.dtype == out.dtype == torch.bfloat16 and pages.is_contiguous()
     tokens = qkv.shape[0]
     need = tokens * nh * splits * (d + 2) * 4 if splits > 1 else 0
@@ -921,7 +925,8 @@ def attention_tc(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile_
         qkv.data_ptr(), qkv.stride(0), pages.data_ptr(), pages.shape[0], block_table.data_ptr(),
         block_table.shape[1], req_indptr.data_ptr(), kv_before.data_ptr(), tile_req.data_ptr(), tile_row.data_ptr(),
         tiles, out.data_ptr(), out.stride(0), nh, nkv, d, page_size, int(window or 0), float(scale), splits,
-        _ptr(token_req), tokens, _ptr(ws), ws_bytes, 1 if defer else 0, _stream())
+        _ptr(token_req), tokens, _ptr(ws), ws_bytes, 1 if defer else 0, float(softcap or 0.0), 1 if sink else 0,
+        _ptr(gate), gate_stride, _stream())
     _check(code, "attention_tc", 2 if splits > 1 and not defer else 1)
     if not defer:
         return None
@@ -929,7 +934,7 @@ def attention_tc(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile_
     def merge() -> None:
         code = _fn("attention_tc", "tl_attention_tc_merge")(
             req_indptr.data_ptr(), out.data_ptr(), out.stride(0), nh, d, splits, token_req.data_ptr(), tokens,
-            ws.data_ptr(), ws_bytes, _stream())
+            ws.data_ptr(), ws_bytes, 1 if sink else 0, _ptr(gate), gate_stride, _stream())
         _check(code, "attention_tc_merge", 1)
 
     return merge

@@ -119,16 +119,15 @@ def _plan(ctx, group_size: int, rows_per_tile: int = ROWS):
 
 def forward(mixer, ctx, qkv, cache, out, gate=None) -> bool:
     """``qkv``: rows whose first ``nh * d`` entries are the (encoded) queries; keys and values are in
-    the cache pages.  A mixer with a score cap (``mixer.softcap``), a sink (``mixer.sink``) or an output
-    ``gate`` runs its prompt portions, too, on the mma.sync kernel, which takes them as arguments."""
+    the cache pages.  A mixer's score cap (``mixer.softcap``), sink (``mixer.sink``) and output ``gate``
+    (float32 rows) are arguments of all three kernels."""
     d, nh, nkv = mixer.head_dim, mixer.num_heads, mixer.num_kv_heads
     group = nh // nkv
     if d not in (64, 128) or group > 16 or qkv.stride(0) % 8:
         return False
     softcap, sink = getattr(mixer, "softcap", None), bool(getattr(mixer, "sink", False))
-    extras = bool(softcap) or sink or gate is not None
     # prompt portions: the tcgen05 kernel where it takes the page size, else the mma.sync kernel
-    use_tc = (not ctx.decode_only) and not extras and ops.attention_tc_supported(d, group, cache.page_size)
+    use_tc = (not ctx.decode_only) and ops.attention_tc_supported(d, group, cache.page_size)
     plan = _plan(ctx, group, ops.attention_tc_rows(group) if use_tc else ROWS)
     common = dict(out=out, tokens=ctx.num_tokens, nh=nh, nkv=nkv, d=d, page_size=cache.page_size,
                   window=mixer.window, scale=mixer.scale, softcap=softcap, sink=sink, gate=gate)
@@ -141,7 +140,8 @@ def forward(mixer, ctx, qkv, cache, out, gate=None) -> bool:
         beside = plan["decode"] is not None and side_by_side(splits, plan["prefill_kv_len"], d)
         merge_portions = ops.attention_tc(
             qkv, cache.pages, cache.block_table, ctx.req_indptr, ctx.kv_before, tile_req, tile_row, count, out, nh, nkv,
-            d, cache.page_size, mixer.window, mixer.scale, splits=splits, token_req=ctx.token_req, defer_merge=beside)
+            d, cache.page_size, mixer.window, mixer.scale, splits=splits, token_req=ctx.token_req, defer_merge=beside,
+            softcap=softcap, sink=sink, gate=gate)
     if plan["decode"] is not None:
         tile_req, count = plan["decode"]
         splits = decode_splits(count, nkv, ctx.max_kv_len, qkv.device)

@@ -78,10 +78,12 @@ struct Params {
 
 __device__ __forceinline__ float capped_tanh(float x) { return 1.f - 2.f / (__expf(2.f * x) + 1.f); }
 // The softmax denominator with the sink's share: a key of score 0 against the running maximum m (log2 units).
-__device__ __forceinline__ float with_sink(const Params& p, float l, float m) {
+template <bool EXTRAS> __device__ __forceinline__ float with_sink(const Params& p, float l, float m) {
+  if constexpr (!EXTRAS) return l;
   return (p.sink && m != -INFINITY) ? l + exp2f(-m) : l;
 }
-__device__ __forceinline__ float gate_of(const Params& p, int token, int head, int D, int c) {
+template <bool EXTRAS> __device__ __forceinline__ float gate_of(const Params& p, int token, int head, int D, int c) {
+  if constexpr (!EXTRAS) return 1.f;
   if (!p.gate) return 1.f;
   return 1.f / (1.f + __expf(-p.gate[(size_t)token * p.gate_stride + (size_t)head * D + c]));
 }
@@ -208,7 +210,7 @@ __device__ __forceinline__ int effective_splits(int splits, int key_tiles) {
 
 // STAGES: key/value tiles in shared memory; 2, or 3 with the TMA loader where the grid leaves
 // room for only two CTAs an SM anyway.
-template <int D, bool ROWS16, bool TMA, int STAGES>
+template <int D, bool ROWS16, bool TMA, int STAGES, bool EXTRAS>
 __global__ void __launch_bounds__(THREADS, STAGES == 2 ? 3 : 2)
 attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) {
   static_assert(!TMA || ROWS16, "the TMA loader serves the 16-row tiles");
@@ -433,7 +435,7 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p)
         const int h = e >> 1;
         const int key = key_base + i * 8 + (lane & 3) * 2 + (e & 1);
         const bool ok = key <= row_pos[h] && key >= row_lo[h];
-        if (p.cap_outer > 0.f)
+        if (EXTRAS && p.cap_outer > 0.f)
           s[i][e] = ok ? capped_tanh(s[i][e] * p.cap_inner) * p.cap_outer : -INFINITY;
         else
           s[i][e] = ok ? s[i][e] * p.scale_log2 : -INFINITY;
@@ -554,7 +556,7 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p)
         }
       } else {
         p.out[(size_t)token * p.out_stride + (size_t)head * D + c] =
-            __float2bfloat16_rn(acc / with_sink(p, l, m_all) * gate_of(p, token, head, D, c));
+            __float2bfloat16_rn(acc / with_sink<EXTRAS>(p, l, m_all) * gate_of<EXTRAS>(p, token, head, D, c));
       }
     }
     if (p.splits > 1 && p.arrivals) {
@@ -607,13 +609,13 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p)
               acc.w = fmaf(v[j].w, f, acc.w);
             }
           }
-          const float inv = 1.f / with_sink(p, l, m_ref);
-          if (p.gate) {
+          const float inv = 1.f / with_sink<EXTRAS>(p, l, m_ref);
+          if (EXTRAS && p.gate) {
             const int head = kvh * g + r;
-            acc.x *= gate_of(p, tok0, head, D, c);
-            acc.y *= gate_of(p, tok0, head, D, c + 1);
-            acc.z *= gate_of(p, tok0, head, D, c + 2);
-            acc.w *= gate_of(p, tok0, head, D, c + 3);
+            acc.x *= gate_of<EXTRAS>(p, tok0, head, D, c);
+            acc.y *= gate_of<EXTRAS>(p, tok0, head, D, c + 1);
+            acc.z *= gate_of<EXTRAS>(p, tok0, head, D, c + 2);
+            acc.w *= gate_of<EXTRAS>(p, tok0, head, D, c + 3);
           }
           uint2 packed;
           packed.x = pack_bf16(acc.x * inv, acc.y * inv);
@@ -628,13 +630,13 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p)
       const int row = row_start + my_rows + (lane >> 2) + 8 * h;
       if (row >= row_end) continue;
       const int token = tok0 + row / g, head = kvh * g + row % g;
-      const float inv = 1.f / with_sink(p, l_run[h], m_run[h]);
+      const float inv = 1.f / with_sink<EXTRAS>(p, l_run[h], m_run[h]);
       __nv_bfloat16* dst = p.out + (size_t)token * p.out_stride + (size_t)head * D + (lane & 3) * 2;
 #pragma unroll
       for (int i = 0; i < DTILES; ++i) {
         const int c = i * 8 + (lane & 3) * 2;
-        *reinterpret_cast<unsigned*>(dst + i * 8) = pack_bf16(o_acc[i][2 * h] * inv * gate_of(p, token, head, D, c),
-                                                              o_acc[i][2 * h + 1] * inv * gate_of(p, token, head, D, c + 1));
+        *reinterpret_cast<unsigned*>(dst + i * 8) = pack_bf16(o_acc[i][2 * h] * inv * gate_of<EXTRAS>(p, token, head, D, c),
+                                                              o_acc[i][2 * h + 1] * inv * gate_of<EXTRAS>(p, token, head, D, c + 1));
       }
     }
   }
@@ -726,7 +728,7 @@ bool cached_map(CUtensorMap* out, const void* base, uint64_t rows, uint32_t cols
   return true;
 }
 
-template <int D, bool ROWS16, bool TMA, int STAGES>
+template <int D, bool ROWS16, bool TMA, int STAGES, bool EXTRAS>
 int launch(const CUtensorMap& map_kv, const Params& p, int tiles, cudaStream_t stream) {
   constexpr int BLOCK_M = ROWS16 ? 16 : 64;
   // 16-row tiles: STAGES key/value stages and Q behind them; 64-row tiles: two stages, Q inside the second.
@@ -737,7 +739,7 @@ int launch(const CUtensorMap& map_kv, const Params& p, int tiles, cudaStream_t s
   static_assert((STAGES == 2 ? 3 : 2) * (SMEM + 1024) <= 227 * 1024, "three CTAs an SM with two stages, two with three");
   static bool configured = false;
   if (!configured) {
-    cudaError_t err = cudaFuncSetAttribute(attention_mma_kernel<D, ROWS16, TMA, STAGES>,
+    cudaError_t err = cudaFuncSetAttribute(attention_mma_kernel<D, ROWS16, TMA, STAGES, EXTRAS>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (err != cudaSuccess) return (int)err;
     configured = true;
@@ -748,7 +750,7 @@ int launch(const CUtensorMap& map_kv, const Params& p, int tiles, cudaStream_t s
   // grids are launched WITHOUT overlap: CTAs that start while the small kernel before them
   // still occupies the SMs are placed unevenly, and a bandwidth-bound grid's time is set by
   // its most loaded SM (measured: batch 64 decode lost 9% with an overlapped launch).
-  tl::launch_kernel_opt(ROWS16 && (tiles <= p.overlap_max_tiles || p.late_wait), attention_mma_kernel<D, ROWS16, TMA, STAGES>, grid, THREADS,
+  tl::launch_kernel_opt(ROWS16 && (tiles <= p.overlap_max_tiles || p.late_wait), attention_mma_kernel<D, ROWS16, TMA, STAGES, EXTRAS>, grid, THREADS,
                         SMEM, stream, map_kv, p);
   return TL_LAUNCH_CHECK();
 }
@@ -774,15 +776,15 @@ int decode_stages() {
   return value;
 }
 
-template <int D>
+template <int D, bool EXTRAS>
 int launch_for(const Params& p, long long num_pages, int tiles, bool rows16, cudaStream_t stream) {
   CUtensorMap map_kv;
   memset(&map_kv, 0, sizeof(map_kv));
-  if (!rows16) return launch<D, false, false, 2>(map_kv, p, tiles, stream);
+  if (!rows16) return launch<D, false, false, 2, EXTRAS>(map_kv, p, tiles, stream);
   const bool tma = decode_tma_enabled() && num_pages > 0 && p.page_size >= 8 && p.page_size % 8 == 0 &&
                    BLOCK_N % p.page_size == 0 &&
                    cached_map(&map_kv, p.pages, (uint64_t)num_pages * 2 * p.nkv * p.page_size, D, (uint32_t)p.page_size);
-  if (!tma) return launch<D, true, false, 2>(map_kv, p, tiles, stream);
+  if (!tma) return launch<D, true, false, 2, EXTRAS>(map_kv, p, tiles, stream);
   // Without key splits (large batches) every CTA walks its request's whole context, and a third
   // stage keeps more of it requested (batch 128 at 2,048 tokens: 7.15 -> 6.68 ms a decode step;
   // batch 64: equal).  With splits the grid is sized for three CTAs an SM, which three stages do
@@ -796,8 +798,8 @@ int launch_for(const Params& p, long long num_pages, int tiles, bool rows16, cud
       sms = 148;
   }
   const bool roomy = p.splits == 1 || (long long)tiles * p.nkv * p.splits <= 2ll * sms;
-  if (decode_stages() == 3 || (decode_stages() == 0 && roomy)) return launch<D, true, true, 3>(map_kv, p, tiles, stream);
-  return launch<D, true, true, 2>(map_kv, p, tiles, stream);
+  if (decode_stages() == 3 || (decode_stages() == 0 && roomy)) return launch<D, true, true, 3, EXTRAS>(map_kv, p, tiles, stream);
+  return launch<D, true, true, 2, EXTRAS>(map_kv, p, tiles, stream);
 }
 
 }  // namespace
@@ -878,8 +880,12 @@ int tl_attention_mma_ex(const void* q, long long q_stride, const void* pages, lo
   p.sink = sink;
   p.gate = gate;
   p.gate_stride = gate_stride;
-  const int rc = d == 128 ? launch_for<128>(p, num_pages, tiles, rows16 != 0, stream)
-                           : launch_for<64>(p, num_pages, tiles, rows16 != 0, stream);
+  // the plain kernels are compiled without the options, so that they cost a model that has none nothing
+  const bool extras = p.cap_outer > 0.f || p.sink || p.gate;
+  const int rc = d == 128 ? (extras ? launch_for<128, true>(p, num_pages, tiles, rows16 != 0, stream)
+                                    : launch_for<128, false>(p, num_pages, tiles, rows16 != 0, stream))
+                          : (extras ? launch_for<64, true>(p, num_pages, tiles, rows16 != 0, stream)
+                                    : launch_for<64, false>(p, num_pages, tiles, rows16 != 0, stream));
   if (rc || splits == 1 || arrivals) return rc;
   const int items = tiles * nh;
   if (d == 128)

@@ -174,7 +174,7 @@ struct RowTile {
   int row_start, row_end, begin, end;
 };
 
-template <int D>
+template <int D, bool EXTRAS>
 __global__ void __launch_bounds__(THREADS, 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) {
   constexpr int TILE_BYTES = TileBytes<D>::value;
@@ -412,11 +412,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
 #pragma unroll
       for (int c = 0; c < KEYS; c += 32) tmem_ld_32(tmem_s + c, reinterpret_cast<uint32_t(&)[32]>(v[c]));
       tmem_ld_wait();
-      if (p.cap_outer > 0.f) {  // capped scores: tanh(s scale / cap), scaled by cap log2(e) below
+      if (EXTRAS && p.cap_outer > 0.f) {  // capped scores: tanh(s scale / cap), scaled by cap log2(e) below
 #pragma unroll
         for (int i = 0; i < KEYS; ++i) v[i] = __float_as_uint(fast_tanh(__uint_as_float(v[i]) * p.cap_inner));
       }
-      const float mult = p.cap_outer > 0.f ? p.cap_outer : p.scale_log2;
+      const float mult = (EXTRAS && p.cap_outer > 0.f) ? p.cap_outer : p.scale_log2;
       // A tile whose keys are all visible to every row of this warp needs no masking; rows beyond
       // the tile's last (zero queries, never stored) take whatever comes
       const bool visible = !row_valid || (key0 + KEYS - 1 <= pos && key0 >= lo);
@@ -496,12 +496,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
     } else if (num_tiles > 0) {
       mbar_wait(&o_done[x], 0, abort_flag, &g_error_word, 9);
       fence_after_sync();
-      if (p.sink && m_ref != -INFINITY) l_sum += exp2f(-m_ref);  // the sink's share: a key of score 0
+      if (EXTRAS && p.sink && m_ref != -INFINITY) l_sum += exp2f(-m_ref);  // the sink's share: a key of score 0
       const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
       __nv_bfloat16* dst = nullptr;
       const float* gate = nullptr;
       if (row_valid) dst = p.out + (size_t)(tok0 + row / g) * p.out_stride + (size_t)(kvh * g + row % g) * D;
-      if (row_valid && p.gate) gate = p.gate + (size_t)(tok0 + row / g) * p.gate_stride + (size_t)(kvh * g + row % g) * D;
+      if (EXTRAS && row_valid && p.gate) gate = p.gate + (size_t)(tok0 + row / g) * p.gate_stride + (size_t)(kvh * g + row % g) * D;
 #pragma unroll 1
       for (int c = 0; c < D; c += 32) {
         uint32_t o[32];
@@ -512,7 +512,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
             float a = __uint_as_float(o[i]) * inv, b = __uint_as_float(o[i + 1]) * inv;
-            if (gate) {
+            if (EXTRAS && gate) {
               a *= 1.f / (1.f + __expf(-gate[c + i]));
               b *= 1.f / (1.f + __expf(-gate[c + i + 1]));
             }
@@ -616,18 +616,18 @@ int launch_merge(const Params& p, const int* token_req, int tokens, cudaStream_t
   return TL_LAUNCH_CHECK();
 }
 
-template <int D>
+template <int D, bool EXTRAS>
 int launch(const CUtensorMap& map_kv, const Params& p, int nkv, int tiles, const int* token_req, int tokens,
            bool defer_merge, cudaStream_t stream) {
   constexpr int SMEM = 6 * TileBytes<D>::value + 1024 + 256;
   static_assert(SMEM <= 232448, "shared memory of one CTA");
   static bool configured = false;
   if (!configured) {
-    cudaError_t err = cudaFuncSetAttribute(attention_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    cudaError_t err = cudaFuncSetAttribute(attention_tc_kernel<D, EXTRAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (err != cudaSuccess) return (int)err;
     configured = true;
   }
-  tl::launch_kernel(attention_tc_kernel<D>, dim3(nkv, tiles, p.splits), THREADS, SMEM, stream, map_kv, p);
+  tl::launch_kernel(attention_tc_kernel<D, EXTRAS>, dim3(nkv, tiles, p.splits), THREADS, SMEM, stream, map_kv, p);
   const int rc = TL_LAUNCH_CHECK();
   if (rc || p.splits == 1 || defer_merge) return rc;
   return launch_merge<D>(p, token_req, tokens, stream);
@@ -702,8 +702,13 @@ int tl_attention_tc(const void* q, long long q_stride, const void* pages, long l
   p.splits = splits;
   p.part_acc = (float*)workspace;
   p.part_ml = p.part_acc + (size_t)(splits > 1 ? tokens : 0) * nh * splits * d;
-  return d == 128 ? launch<128>(map_kv, p, nkv, tiles, token_req, tokens, defer_merge != 0, stream)
-                  : launch<64>(map_kv, p, nkv, tiles, token_req, tokens, defer_merge != 0, stream);
+  // the plain kernels are compiled without the options, so that they cost a model that has none nothing
+  const bool merge_later = defer_merge != 0;
+  if (p.cap_outer > 0.f || p.sink || p.gate)
+    return d == 128 ? launch<128, true>(map_kv, p, nkv, tiles, token_req, tokens, merge_later, stream)
+                    : launch<64, true>(map_kv, p, nkv, tiles, token_req, tokens, merge_later, stream);
+  return d == 128 ? launch<128, false>(map_kv, p, nkv, tiles, token_req, tokens, merge_later, stream)
+                  : launch<64, false>(map_kv, p, nkv, tiles, token_req, tokens, merge_later, stream);
 }
 
 // The merge that a tl_attention_tc call with defer_merge left undone: same out, sizes, splits,

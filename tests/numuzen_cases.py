@@ -51,12 +51,13 @@ CASES = {
               layer("attention", attn(4, 2, 24, 0.3, window=37, softcap=5.0, rot_dims=8, base=500.0, scaling=YARN)),
               layer("gla", gla(2, 24, 8, 9.0, 5), experts=2, top=1, ff=56, limit=3.0),
           ]},
-    # one head, one expert of one, all experts of three, a window of ONE token, no cap, full rotation, no scaling
+    # one head, one expert of one, all experts of three, a window of ONE token, no cap, full rotation, no scaling,
+    # a head size that is no multiple of 8, no window
     "Q": {"architecture": "Numuzen", "vocab": 67, "width": 64, "norm": {"eps": 1e-6},
           "layers": [
               layer("gla", gla(1, 40, 8, 1.0, 3), experts=1, top=1, ff=24, limit=0.7),
               layer("attention", attn(2, 2, 16, 0.25, window=1, rot_dims=16, base=100.0), experts=3, top=3, ff=24),
-              layer("attention", attn(1, 1, 32, 0.2, rot_dims=2, base=100.0), experts=3, top=3, ff=24),
+              layer("attention", attn(3, 1, 20, 0.2, rot_dims=6, base=100.0), experts=3, top=3, ff=24),
               layer("gla", gla(5, 8, 16, 32.0, 7)),
           ]},
     # sizes the tensor-core kernels take: heads of 64 and 128, windows of several pages

@@ -10,8 +10,9 @@
 // softmax's denominator (a key of score 0 that has no value); ``gate`` (float32 rows) multiplies the
 // output element by element with sigmoid(gate).
 //
-// This is the true 32-bit kernel and the any-size bfloat16 kernel (head_dim any
-// multiple of 8 up to 256, any head counts, any page size).
+// This is the true 32-bit kernel and the any-size bfloat16 kernel (head_dim up to 256: keys are
+// read eight entries at a time where head_dim and the query stride are multiples of 8, one at a
+// time otherwise; any head counts, any page size).
 //
 // Reference counterparts: forward_ragged_attention_kernel and
 // forward_slot_attention_decode_kernel, v10_triton_paged_gqa/kernel/gqa.py:5-228
@@ -35,7 +36,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restr
                          const int* __restrict__ token_req, const int* __restrict__ positions,
                          T* __restrict__ out, int out_stride, int tokens, int nh, int nkv, int d,
                          int page_size, int window, float scale, int num_pages, float softcap, int sink,
-                         const float* __restrict__ gate, int gate_stride) {
+                         const float* __restrict__ gate, int gate_stride, int wide) {
   tl::pdl_wait();               // everything before us in the stream is complete and visible
   tl::pdl_launch_dependents();  // the next kernel may start its own prologue
 
@@ -76,11 +77,15 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restr
       row_off = (size_t)page * page_elems + (size_t)(key % page_size) * d;
       const T* krow = pages + row_off + k_off;
       float dot = 0.f;
-      for (int i = 0; i < d; i += 8) {
-        float kv[8];
-        load8(krow + i, kv);
+      if (wide) {
+        for (int i = 0; i < d; i += 8) {
+          float kv[8];
+          load8(krow + i, kv);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) dot = fmaf(qs[warp][i + j], kv[j], dot);
+          for (int j = 0; j < 8; ++j) dot = fmaf(qs[warp][i + j], kv[j], dot);
+        }
+      } else {  // the same order of additions, one entry at a time
+        for (int i = 0; i < d; ++i) dot = fmaf(qs[warp][i], to_float(krow[i]), dot);
       }
       s = dot * scale;
       if (softcap > 0.f) s = softcap * tanhf(s / softcap);
@@ -129,19 +134,19 @@ extern "C" int tl_attention_generic(const void* q, int q_stride, const void* pag
                                     int num_pages, float softcap, int sink, const float* gate, int gate_stride,
                                     cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (d <= 0 || d > MAX_D || d % 8 || nkv <= 0 || nh % nkv || page_size <= 0 || q_stride % 8)
-    return TL_ERR_UNSUPPORTED;
+  if (d <= 0 || d > MAX_D || nkv <= 0 || nh % nkv || page_size <= 0) return TL_ERR_UNSUPPORTED;
+  const int wide = d % 8 == 0 && q_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(pages) & 31) == 0;
   const long long items = (long long)tokens * nh;
   const unsigned blocks = (unsigned)((items + WARPS - 1) / WARPS);
   if (dtype == TL_DTYPE_F32)
     tl::launch_kernel(attention_generic_kernel<float>, blocks, WARPS * 32, 0, stream, 
         (const float*)q, q_stride, (const float*)pages, block_table, table_width, token_req,
         positions, (float*)out, out_stride, tokens, nh, nkv, d, page_size, window, scale, num_pages, softcap, sink,
-        gate, gate_stride);
+        gate, gate_stride, wide);
   else
     tl::launch_kernel(attention_generic_kernel<__nv_bfloat16>, blocks, WARPS * 32, 0, stream, 
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)pages, block_table, table_width,
         token_req, positions, (__nv_bfloat16*)out, out_stride, tokens, nh, nkv, d, page_size, window,
-        scale, num_pages, softcap, sink, gate, gate_stride);
+        scale, num_pages, softcap, sink, gate, gate_stride, wide);
   return TL_LAUNCH_CHECK();
 }

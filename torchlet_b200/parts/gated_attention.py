@@ -57,8 +57,8 @@ class GatedAttentionMixer(Mixer):
             raise ValueError(f"unknown gate {self.gate!r} (known: 'sigmoid', None)")
         if self.num_heads % self.num_kv_heads:
             raise ValueError("num_heads must be divisible by num_kv_heads")
-        if self.head_dim % 8 or self.head_dim > 256:
-            raise ValueError(f"head_dim {self.head_dim} is not supported (multiples of 8 up to 256)")
+        if self.head_dim > 256:
+            raise ValueError(f"head_dim {self.head_dim} is not supported (up to 256)")
         self.positions = build_part(POSITIONS, p["positions"]) if p.get("positions") else None
         if self.positions is not None and not hasattr(self.positions, "inv_freq"):
             raise ValueError("this mixer rotates inside its own kernel and needs a position part with a frequency table")

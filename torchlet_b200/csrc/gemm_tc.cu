@@ -230,7 +230,17 @@ gemm_tc_swapped_kernel(const __grid_constant__ CUtensorMap map_row, const __grid
   const int row0 = blockIdx.x * BLOCK_P, col0 = blockIdx.y * BLOCK_Q;
   const int kb_begin = blockIdx.z * p.k_blocks_per_split;
   const int kb_end = min(p.k_blocks, kb_begin + p.k_blocks_per_split);
-  const int num_kb = kb_end - kb_begin;
+  int num_kb = kb_end - kb_begin;
+  // Grouped product: column tile blockIdx.y (BLOCK_Q group-sorted rows) belongs to ONE group, whose weights
+  // are rows [g group_rows, (g + 1) group_rows) of the row operand.  The plan is written by an earlier kernel,
+  // so nothing is requested before the wait; a tile that is not in use runs no k-block and writes nothing.
+  int wrow0 = row0;
+  if (p.plan) {
+    tl::pdl_wait();
+    const int group = (int)blockIdx.y < p.plan[0] ? p.plan[1 + blockIdx.y] : -1;
+    if (group < 0) num_kb = 0;
+    else wrow0 = group * p.group_rows + row0;
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -262,7 +272,7 @@ gemm_tc_swapped_kernel(const __grid_constant__ CUtensorMap map_row, const __grid
       const int ahead = min(min(STAGES, p.ahead), num_kb);
       for (int it = 0; it < ahead; ++it) {
         mbar_expect_tx(&full[it], STAGE_BYTES);
-        tma_load_2d(smem + it * STAGE_BYTES, &map_row, &full[it], (kb_begin + it) * BLOCK_K, row0);
+        tma_load_2d(smem + it * STAGE_BYTES, &map_row, &full[it], (kb_begin + it) * BLOCK_K, wrow0);
       }
       tl::pdl_wait();
       for (int it = 0; it < ahead; ++it)
@@ -274,7 +284,7 @@ gemm_tc_swapped_kernel(const __grid_constant__ CUtensorMap map_row, const __grid
         mbar_expect_tx(&full[s], STAGE_BYTES);
         uint8_t* stage = smem + s * STAGE_BYTES;
         const int k = (kb_begin + it) * BLOCK_K;
-        tma_load_2d(stage, &map_row, &full[s], k, row0);
+        tma_load_2d(stage, &map_row, &full[s], k, wrow0);
         tma_load_2d(stage + ROW_TILE_BYTES, &map_col, &full[s], k, col0);
       }
     } else {
@@ -1169,10 +1179,42 @@ static int gemm_tc_impl(const void* x, const void* w, const float* bias, void* o
 // plan[1 + i], plan[0] tiles are in use), w [groups * N, K] (group g's matrix in rows [g N, (g + 1) N)),
 // out [rows, N] (or [rows, N / 2] with the gated epilogue over 16-interleaved gate / up rows).  The plan is
 // read on the device, so nothing comes back to the host; tiles that are not in use cost nothing.
+// tile_rows: 128 (the persistent kernel; row tiles of 128 sorted rows), or 16 for few rows a group (the
+// weight-streaming orientation: a CTA takes 128 weight rows of a tile's group and the tile's 16 sorted rows, so
+// that the shared memory holds weights in flight and not padding rows).
 int tl_gemm_tc_grouped(const void* x, const void* w, void* out, long long ldo, int epilogue, int rows, int N, int K,
-                       int groups, const int* plan, float glu_limit, float glu_alpha, cudaStream_t stream) {
+                       int groups, const int* plan, int tile_rows, float glu_limit, float glu_alpha,
+                       cudaStream_t stream) {
   if (rows <= 0 || N <= 0 || groups <= 0) return 0;
-  if (K <= 0 || K % 8 || rows % BLOCK_P || !plan || epilogue < 0 || epilogue > 3) return TL_ERR_UNSUPPORTED;
+  if (K <= 0 || K % 8 || !plan || epilogue < 0 || epilogue > 3 || (tile_rows != BLOCK_P && tile_rows != 16) ||
+      rows % tile_rows)
+    return TL_ERR_UNSUPPORTED;
+  if (tile_rows == 16) {
+    if (epilogue == EPI_SWIGLU_BF16 && N % 32) return TL_ERR_UNSUPPORTED;
+    if (epilogue == EPI_ACCUM_F32 || rows / 16 > 65535) return TL_ERR_UNSUPPORTED;
+    Params p;
+    p.k_blocks = p.k_blocks_per_split = (K + BLOCK_K - 1) / BLOCK_K;
+    p.bias = nullptr;
+    p.out = out;
+    p.ldo = ldo;
+    p.epilogue = epilogue;
+    p.partial = nullptr;
+    p.splits = 1;
+    p.ahead = 8;
+    p.glu_limit = glu_limit;
+    p.glu_alpha = glu_alpha;
+    p.plan = plan;
+    p.group_rows = N;
+    p.rows = N;     // weight rows of one group
+    p.cols = rows;  // sorted rows
+    p.block_q = 16;
+    p.stages = 6;
+    p.row_tiles = p.num_tiles = 0;
+    CUtensorMap map_row, map_col;
+    if (!cached_map(&map_row, w, (uint64_t)groups * N, K, K, BLOCK_P) || !cached_map(&map_col, x, rows, K, K, 16))
+      return TL_ERR_UNSUPPORTED;
+    return launch_swapped<16, 6>(map_row, map_col, p, dim3((N + BLOCK_P - 1) / BLOCK_P, rows / 16, 1), stream);
+  }
   if (epilogue == EPI_SWIGLU_BF16 && N % 32) return TL_ERR_UNSUPPORTED;
   if (epilogue == EPI_ACCUM_F32) return TL_ERR_UNSUPPORTED;
   Params p;

@@ -55,8 +55,8 @@ _SIGNATURES = {
                        c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p],
         "tl_gemm_tc_glu": [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_longlong, c_longlong, c_void_p,
                            c_longlong, c_float, c_float, c_void_p],
-        "tl_gemm_tc_grouped": [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float,
-                               c_float, c_void_p],
+        "tl_gemm_tc_grouped": [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
+                               c_float, c_float, c_void_p],
         "tl_gemm_tc_plan": [c_int, c_int, c_int, c_void_p, c_void_p],
         "tl_gemm_tc_error": [],
         "tl_gemm_tc_wait_selftest": [c_int, c_void_p],
@@ -758,11 +758,14 @@ def gemm_tc_glu(x, w, out, limit: float, alpha: float) -> None:
 
 
 GROUPED_TILE_ROWS = 128  # rows of a tile of the grouped tcgen05 product: every group's rows are padded to these
+GROUPED_TILE_ROWS_FEW = 16  # ... and where a group has few rows (the weight-streaming orientation)
 
 
-def gemm_tc_grouped(x, w, out, plan, glu: bool = False, limit: float = 0.0, alpha: float = 0.0) -> None:
-    """Grouped product over group-sorted rows on the tcgen05 tensor cores (the persistent kernel of
-    csrc/gemm_tc.cu with a plan): out[r] = W_g(r) x[r].  ``x`` [rows, K] bfloat16 with rows = 128 * tiles;
+def gemm_tc_grouped(x, w, out, plan, glu: bool = False, limit: float = 0.0, alpha: float = 0.0,
+                    tile_rows: int = GROUPED_TILE_ROWS) -> None:
+    """Grouped product over group-sorted rows on the tcgen05 tensor cores (csrc/gemm_tc.cu with a plan):
+    out[r] = W_g(r) x[r].  ``x`` [rows, K] bfloat16 with rows = tile_rows * tiles; ``tile_rows`` 128 (the
+    persistent kernel) or 16 (few rows a group: the weight-streaming orientation);
     ``plan`` int32 [1 + tiles] on the device: plan[0] tiles in use, plan[1 + i] the group of row tile i;
     ``w`` [groups, N, K]; ``out`` [rows, N] float32 or bfloat16, or with ``glu`` (``w`` [groups, 2 F, K], gate
     and up rows interleaved by 16) [rows, F] bfloat16 with the clamped gated activation applied."""
@@ -771,7 +774,7 @@ def gemm_tc_grouped(x, w, out, plan, glu: bool = False, limit: float = 0.0, alph
     rows, K = x.shape
     groups, N = w.shape[0], w.shape[1]
     assert x.dtype == w.dtype == torch.bfloat16 and x.is_contiguous() and w.is_contiguous() and w.shape[2] == K
-    assert rows == (plan.numel() - 1) * GROUPED_TILE_ROWS == out.shape[0] and plan.dtype == torch.int32
+    assert rows == (plan.numel() - 1) * tile_rows == out.shape[0] and plan.dtype == torch.int32
     assert out.stride(1) == 1 and out.shape[1] == (N // 2 if glu else N)
     if glu:
         assert out.dtype == torch.bfloat16
@@ -780,7 +783,7 @@ def gemm_tc_grouped(x, w, out, plan, glu: bool = False, limit: float = 0.0, alph
         epilogue = EPI_STORE_BF16 if out.dtype == torch.bfloat16 else EPI_STORE_F32
     code = _fn("gemm_tc", "tl_gemm_tc_grouped")(
         x.data_ptr(), w.data_ptr(), out.data_ptr(), out.stride(0), epilogue, rows, N, K, groups, plan.data_ptr(),
-        float(limit), float(alpha), _stream())
+        tile_rows, float(limit), float(alpha), _stream())
     _check(code, "gemm_tc_grouped")
 
 

@@ -86,10 +86,20 @@ class RoutedClampedGLU(FeedForward):
 
     def forward(self, ctx, x, acc) -> None:
         tokens, top, E = x.shape[0], self.top_k, self.num_experts
-        tile = ops.GROUPED_TILE_ROWS if self.tensor_cores else ops.moe_tile_rows()
+        # tiles of 128 sorted rows on the tensor cores, of 16 where an expert gets 16 rows or fewer on average
+        # (steps of single tokens: the products then stream the chosen experts' weights); 64 on CUDA cores
+        if not self.tensor_cores:
+            tile = ops.moe_tile_rows()
+        elif tokens * top <= ops.GROUPED_TILE_ROWS_FEW * E:
+            tile = ops.GROUPED_TILE_ROWS_FEW
+        else:
+            tile = ops.GROUPED_TILE_ROWS
         tiles, rows = self._rows(tokens, tile)
-        # scratch sized once for the largest step, so that its addresses never change
-        most_tiles, most_rows = self._rows(max(ctx.token_capacity, tokens), tile)
+        # scratch sized once for the largest step (and the tile size that takes most), so that its addresses never change
+        capacity = max(ctx.token_capacity, tokens)
+        few = self._rows(min(capacity, ops.GROUPED_TILE_ROWS_FEW * E // top), ops.GROUPED_TILE_ROWS_FEW)
+        most = self._rows(capacity, tile if not self.tensor_cores else ops.GROUPED_TILE_ROWS)
+        most_tiles, most_rows = max(few[0], most[0]), max(few[1], most[1])
         choice = ctx.buffer("moe.choice", (tokens, top), torch.int32)
         weight = ctx.buffer("moe.weight", (tokens, top), torch.float32)
         position = ctx.buffer("moe.position", (tokens, top), torch.int32)
@@ -102,8 +112,9 @@ class RoutedClampedGLU(FeedForward):
         ops.moe_plan(choice, position, plan, E, tile)
         ops.moe_scatter(x, position, weight, sorted_x, top, weighted=on_input)
         if self.tensor_cores:
-            ops.gemm_tc_grouped(sorted_x, self.gate_up, act, plan, glu=True, limit=self.limit, alpha=self.alpha)
-            ops.gemm_tc_grouped(act, self.down, y, plan)
+            ops.gemm_tc_grouped(sorted_x, self.gate_up, act, plan, glu=True, limit=self.limit, alpha=self.alpha,
+                                tile_rows=tile)
+            ops.gemm_tc_grouped(act, self.down, y, plan, tile_rows=tile)
         else:
             ops.moe_gemm_simt(sorted_x, self.gate_up, act, plan, glu=True, limit=self.limit, alpha=self.alpha)
             ops.moe_gemm_simt(act, self.down, y, plan)

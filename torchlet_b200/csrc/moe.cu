@@ -29,40 +29,26 @@ using namespace tl;
 constexpr int ROUTE_WARPS = 8;
 constexpr int MAX_EXPERTS = 256;
 
-// One block per token.  The token's row is staged in shared memory as floats; warp w takes the
-// experts w, w + 8, ...: each lane sums its 32nd of the row in four independent chains (k = lane,
-// lane + 32, ... in turn), so a logit's order of additions depends on the width alone.
-template <typename T>
-__global__ void __launch_bounds__(ROUTE_WARPS * 32)
-moe_route_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ router, int* __restrict__ choice,
-                 float* __restrict__ weight, int tokens, int hidden, int experts, int top, int softmax_scores,
-                 int renormalize) {
-  tl::pdl_launch_dependents();
-  tl::pdl_wait();
-  extern __shared__ float xrow[];  // hidden floats
-  __shared__ float all_scores[MAX_EXPERTS];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x;
-  const T* row = x + (size_t)t * ldx;
-  for (int k = threadIdx.x; k < hidden; k += ROUTE_WARPS * 32) xrow[k] = to_float(row[k]);
-  __syncthreads();
-  for (int e = warp; e < experts; e += ROUTE_WARPS) {
-    const float* w = router + (size_t)e * hidden;
-    float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
-    int k = lane;
-    for (; k + 96 < hidden; k += 128) {
-      p0 = fmaf(xrow[k], w[k], p0);
-      p1 = fmaf(xrow[k + 32], w[k + 32], p1);
-      p2 = fmaf(xrow[k + 64], w[k + 64], p2);
-      p3 = fmaf(xrow[k + 96], w[k + 96], p3);
-    }
-    for (; k < hidden; k += 32) p0 = fmaf(xrow[k], w[k], p0);
-    const float part = warp_sum((p0 + p1) + (p2 + p3));
-    if (lane == 0) all_scores[e] = part;
+// One router logit by one warp: each lane sums its 32nd of the row in four independent chains (k = lane,
+// lane + 32, ... in turn), so a logit's order of additions depends on the width alone, whichever kernel asks.
+template <typename Row>
+__device__ __forceinline__ float router_logit(const Row* __restrict__ row, const float* __restrict__ w, int hidden, int lane) {
+  float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
+  int k = lane;
+  for (; k + 96 < hidden; k += 128) {
+    p0 = fmaf(to_float(row[k]), w[k], p0);
+    p1 = fmaf(to_float(row[k + 32]), w[k + 32], p1);
+    p2 = fmaf(to_float(row[k + 64]), w[k + 64], p2);
+    p3 = fmaf(to_float(row[k + 96]), w[k + 96], p3);
   }
-  __syncthreads();
-  if (warp != 0) return;
-  float* score = all_scores;  // the first warp alone goes on: scores, the choice, the weights
+  for (; k < hidden; k += 32) p0 = fmaf(to_float(row[k]), w[k], p0);
+  return warp_sum((p0 + p1) + (p2 + p3));
+}
+
+// One warp: from a token's router logits (``score``, shared memory, overwritten) to its ``top`` experts and
+// their weights.
+__device__ __forceinline__ void choose_experts(float* score, int experts, int top, int softmax_scores, int renormalize,
+                                               int lane, int* __restrict__ choice, float* __restrict__ weight) {
   if (softmax_scores) {
     float m = -INFINITY;
     for (int e = lane; e < experts; e += 32) m = fmaxf(m, score[e]);
@@ -92,15 +78,40 @@ moe_route_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ rou
     if (at >= experts) at = 0;  // every score was NaN: still a valid expert
     total += best;
     if (lane == 0) {
-      choice[(size_t)t * top + j] = at;
-      weight[(size_t)t * top + j] = best;
+      choice[j] = at;
+      weight[j] = best;
       score[at] = -INFINITY;
     }
     __syncwarp();
   }
-  if (renormalize && lane < top) weight[(size_t)t * top + lane] /= total;
   if (renormalize)
-    for (int j = 32 + lane; j < top; j += 32) weight[(size_t)t * top + j] /= total;
+    for (int j = lane; j < top; j += 32) weight[j] /= total;
+}
+
+// One block per token.  The token's row is staged in shared memory as floats; warp w takes the
+// experts w, w + 8, ...; the first warp then chooses.
+template <typename T>
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+moe_route_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ router, int* __restrict__ choice,
+                 float* __restrict__ weight, int tokens, int hidden, int experts, int top, int softmax_scores,
+                 int renormalize) {
+  tl::pdl_launch_dependents();
+  tl::pdl_wait();
+  extern __shared__ float xrow[];  // hidden floats
+  __shared__ float all_scores[MAX_EXPERTS];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x;
+  const T* row = x + (size_t)t * ldx;
+  for (int k = threadIdx.x; k < hidden; k += ROUTE_WARPS * 32) xrow[k] = to_float(row[k]);
+  __syncthreads();
+  for (int e = warp; e < experts; e += ROUTE_WARPS) {
+    const float part = router_logit(xrow, router + (size_t)e * hidden, hidden, lane);
+    if (lane == 0) all_scores[e] = part;
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  choose_experts(all_scores, experts, top, softmax_scores, renormalize, lane, choice + (size_t)t * top,
+                 weight + (size_t)t * top);
 }
 
 // plan[0] = tiles in use; plan[1 ..] = expert of every tile (-1: none).

@@ -95,6 +95,39 @@ rms_scaled_add_kernel(float* __restrict__ acc, float* __restrict__ y, const floa
   }
 }
 
+// The same for a sub-layer output of which a product left ``splits`` partial sums [splits][rows][hidden]:
+// v = y + their sum in ascending order, acc[r] += m * v * rsqrt(mean(v^2) + eps) * w; ``clear``: y is left zeroed.  The sums are taken twice
+// (once for the mean square, once for the output) rather than kept: the partial sums of a step of few tokens
+// lie in the L2.
+template <int NT>
+__global__ void __launch_bounds__(NT)
+rms_scaled_add_partials_kernel(float* __restrict__ acc, float* __restrict__ y, const float* __restrict__ partials,
+                               int splits, int rows, const float* __restrict__ w, float m, float eps, int hidden,
+                               int clear) {
+  tl::pdl_launch_dependents();
+  tl::pdl_wait();
+  __shared__ float scratch[32];
+  const size_t plane = (size_t)rows * hidden;
+  const float* row = partials + (size_t)blockIdx.x * hidden;
+  float* yrow = y + (size_t)blockIdx.x * hidden;
+  float* out = acc + (size_t)blockIdx.x * hidden;
+  float ss = 0.f;
+  for (int j = threadIdx.x; j < hidden; j += NT) {
+    float v = yrow[j];
+    for (int s = 0; s < splits; ++s) v += row[(size_t)s * plane + j];
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum<NT>(ss, scratch);
+  const float inv = rsqrtf(ss / (float)hidden + eps);
+  for (int j = threadIdx.x; j < hidden; j += NT) {
+    float v = yrow[j];
+    for (int s = 0; s < splits; ++s) v += row[(size_t)s * plane + j];
+    out[j] = fmaf(m, v * inv * w[j], out[j]);
+    if (clear) yrow[j] = 0.f;
+    else yrow[j] = v;  // y holds the finished sum, as after a finishing pass of its own
+  }
+}
+
 __device__ __forceinline__ float gelu_tanh(float z) {
   return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
@@ -174,6 +207,19 @@ int tl_rms_scaled_add(float* acc, float* y, const float* w, float m, float eps, 
     tl::launch_kernel(rms_scaled_add_kernel<128>, rows, 128, 0, stream, acc, y, w, m, eps, hidden, clear);
   else
     tl::launch_kernel(rms_scaled_add_kernel<512>, rows, 512, 0, stream, acc, y, w, m, eps, hidden, clear);
+  return TL_LAUNCH_CHECK();
+}
+
+int tl_rms_scaled_add_partials(float* acc, float* y, const float* partials, int splits, const float* w, float m, float eps,
+                               int rows, int hidden, int clear, cudaStream_t stream) {
+  if (rows <= 0 || hidden <= 0) return 0;
+  if (splits <= 0) return TL_ERR_UNSUPPORTED;
+  if (hidden <= 1024)
+    tl::launch_kernel(rms_scaled_add_partials_kernel<128>, rows, 128, 0, stream, acc, y, partials, splits, rows, w, m, eps,
+                      hidden, clear);
+  else
+    tl::launch_kernel(rms_scaled_add_partials_kernel<512>, rows, 512, 0, stream, acc, y, partials, splits, rows, w, m, eps,
+                      hidden, clear);
   return TL_LAUNCH_CHECK();
 }
 

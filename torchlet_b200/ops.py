@@ -102,6 +102,8 @@ _SIGNATURES = {
         "tl_scale": [c_void_p, c_float, c_longlong, c_void_p],
         "tl_scaled_add": [c_void_p, c_void_p, c_float, c_void_p, c_longlong, c_void_p],
         "tl_rms_scaled_add": [c_void_p, c_void_p, c_void_p, c_float, c_float, c_int, c_int, c_int, c_void_p],
+        "tl_rms_scaled_add_partials": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_float, c_float, c_int, c_int, c_int,
+                                       c_void_p],
         "tl_gated_token_embed": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
         "tl_clamped_glu": [c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p],
         "tl_stream_ops_debug_error": [c_void_p],
@@ -359,6 +361,22 @@ def rms_scaled_add(acc: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, m: 
     code = _fn("stream_ops", "tl_rms_scaled_add")(acc.data_ptr(), y.data_ptr(), weight.data_ptr(), float(m),
                                                   float(eps), rows, hidden, 1 if clear else 0, _stream())
     _check(code, "rms_scaled_add")
+
+
+def rms_scaled_add_partials(acc: torch.Tensor, y: torch.Tensor, partials: torch.Tensor, splits: int, weight: torch.Tensor,
+                            m: float, eps: float, clear: bool = False) -> None:
+    """``rms_scaled_add`` for a y that still lacks ``splits`` float32 partial sums [splits, rows, hidden] (the start
+    of ``partials``) which a product left: they are added inside the kernel (y then holds the sum, or zeros with
+    ``clear``)."""
+    _need_cuda(acc, y, partials, weight)
+    rows, hidden = acc.shape
+    assert acc.dtype == y.dtype == partials.dtype == weight.dtype == torch.float32 and acc.is_contiguous()
+    assert y.is_contiguous() and y.shape == acc.shape
+    assert partials.numel() >= splits * rows * hidden and weight.numel() == hidden
+    code = _fn("stream_ops", "tl_rms_scaled_add_partials")(acc.data_ptr(), y.data_ptr(), partials.data_ptr(), splits,
+                                                           weight.data_ptr(), float(m), float(eps), rows, hidden,
+                                                           1 if clear else 0, _stream())
+    _check(code, "rms_scaled_add_partials")
 
 
 def gated_token_embed(gate: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:

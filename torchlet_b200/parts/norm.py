@@ -64,7 +64,12 @@ class RMSNorm(Norm):
         if self.groups != 1:
             raise ValueError("the norm of a sub-layer's output is not built for grouped norms")
         pending = ctx.take_pending(y)
-        if pending is not None:  # the sub-layer's last product left its split sums: finish them into y first
+        if pending is not None and pending.bias is None:
+            # the sub-layer's last product left its split sums: their sum into y, the norm and the residual sum
+            # as one kernel
+            ops.rms_scaled_add_partials(acc, y, pending.partials, pending.splits, self.weight, m, self.eps, clear)
+            return
+        if pending is not None:  # finish the split sums into y first
             ops.finish_accum_norm(pending.partials, pending.splits, pending.bias, y)
         else:
             ctx.flush_pending()

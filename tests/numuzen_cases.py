@@ -33,7 +33,7 @@ def attn(heads, kv_heads, dim, scale, window=None, softcap=None, rot_dims=None, 
     return mixer
 
 
-def layer(kind, mixer, experts=None, top=None, ff=None, limit=2.0):
+def layer(kind, mixer, experts=None, top=None, ff=None, limit=1.5):
     mlp = None if experts is None else {"kind": "moe", "expert": {"ff": ff, "limit": limit},
                                         "router": {"experts": experts, "top": top}}
     return {"type": kind, "mixer": mixer, "mlp": mlp}
@@ -63,12 +63,12 @@ CASES = {
     # sizes the tensor-core kernels take: heads of 64 and 128, windows of several pages
     "R": {"architecture": "Numuzen", "vocab": 211, "width": 128, "norm": {"eps": 1e-6},
           "layers": [
-              layer("gla", gla(2, 64, 64, 16.0, 16), experts=4, top=2, ff=64, limit=2.0),
+              layer("gla", gla(2, 64, 64, 12.0, 16), experts=4, top=2, ff=64, limit=1.5),
               layer("attention", attn(4, 1, 64, 0.125, window=150, softcap=20.0, rot_dims=32, base=50000.0, scaling=YARN),
-                    experts=4, top=2, ff=64, limit=2.0),
-              layer("attention", attn(6, 2, 128, 0.09, window=70, softcap=30.0, rot_dims=64, base=50000.0),
-                    experts=4, top=1, ff=128, limit=2.0),
-              layer("gla", gla(1, 128, 32, 8.0, 8), experts=4, top=2, ff=64, limit=2.0),
+                    experts=4, top=2, ff=64, limit=1.5),
+              layer("attention", attn(6, 2, 128, 0.09, window=70, softcap=25.0, rot_dims=64, base=50000.0),
+                    experts=4, top=1, ff=128, limit=2.5),
+              layer("gla", gla(1, 128, 32, 8.0, 8), experts=4, top=2, ff=64, limit=1.5),
           ]},
 }
 

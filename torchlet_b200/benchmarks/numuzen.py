@@ -28,14 +28,14 @@ def numuzen_config(size: str, layers: int, experts: int = 8, top: int = 2, windo
     which a token uses ``top``, each 1 / top of the dense models' feed-forward width."""
     if size == "2b":
         width, ff, vocab = 2048, 8192, 32768
-        gla = {"heads": 16, "dim": 64, "vdim": 128, "tau": 16.0, "decay_rank": 32}
+        gla = {"heads": 16, "dim": 64, "vdim": 128, "tau": 12.0, "decay_rank": 32}
         attention = {"heads": 16, "kv_heads": 4, "dim": 128, "vdim": 128}
     else:
         width, ff, vocab = 1024, 4096, 32768
-        gla = {"heads": 8, "dim": 64, "vdim": 128, "tau": 16.0, "decay_rank": 16}
+        gla = {"heads": 8, "dim": 64, "vdim": 128, "tau": 12.0, "decay_rank": 16}
         attention = {"heads": 16, "kv_heads": 4, "dim": 64, "vdim": 64}
-    attention.update(scale=attention["dim"] ** -0.5, softcap=30.0, mask={"size": window},
-                     rot={"base": 500000.0, "dims": attention["dim"] // 2,
+    attention.update(scale=attention["dim"] ** -0.5, softcap=50.0, mask={"size": window},
+                     rot={"base": 1000000.0, "dims": attention["dim"] // 2,
                           "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}})
     mlp = {"kind": "moe", "expert": {"ff": ff // top, "limit": 7.0}, "router": {"experts": experts, "top": top}}
     out = [{"type": "attention" if i % 2 else "gla", "mixer": dict(attention if i % 2 else gla), "mlp": mlp}

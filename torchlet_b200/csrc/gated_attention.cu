@@ -17,9 +17,9 @@ namespace {
 
 using namespace tl;
 
-constexpr int NT = 256;
-
-template <typename T>
+// NT threads a token: 256 up to 1,024 entries of q and k together, 512 up to 4,096, 1,024 beyond, so that a thread
+// walks few entries one after the other.
+template <typename T, int NT>
 __global__ void __launch_bounds__(NT)
 normed_qk_store_kernel(const float* __restrict__ proj, int proj_stride, const float* __restrict__ wq,
                        const float* __restrict__ wk, const float* __restrict__ inv_freq, float magnitude, float eps,
@@ -99,13 +99,20 @@ extern "C" int tl_normed_qk_store(const float* proj, int proj_stride, const floa
                                   int norm_q, int norm_k, int v_offset, int write_kv, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (d <= 0 || dims < 0 || dims > d || dims % 2 || nh <= 0 || nkv <= 0 || page_size <= 0) return TL_ERR_UNSUPPORTED;
-  if (dtype == TL_DTYPE_F32)
-    tl::launch_kernel(normed_qk_store_kernel<float>, (unsigned)tokens, NT, 0, stream, proj, proj_stride, wq, wk, inv_freq,
-                      magnitude, eps, positions, token_req, block_table, table_width, (float*)pages, page_size, num_pages,
-                      (float*)q_out, nh, nkv, d, dims, norm_q, norm_k, v_offset, write_kv);
-  else
-    tl::launch_kernel(normed_qk_store_kernel<__nv_bfloat16>, (unsigned)tokens, NT, 0, stream, proj, proj_stride, wq, wk,
-                      inv_freq, magnitude, eps, positions, token_req, block_table, table_width, (__nv_bfloat16*)pages,
-                      page_size, num_pages, (__nv_bfloat16*)q_out, nh, nkv, d, dims, norm_q, norm_k, v_offset, write_kv);
+  const long long width = (long long)(nh + nkv) * d;
+#define TL_STORE(T, NT)                                                                                              \
+  tl::launch_kernel(normed_qk_store_kernel<T, NT>, (unsigned)tokens, NT, 0, stream, proj, proj_stride, wq, wk, inv_freq, \
+                    magnitude, eps, positions, token_req, block_table, table_width, (T*)pages, page_size, num_pages,     \
+                    (T*)q_out, nh, nkv, d, dims, norm_q, norm_k, v_offset, write_kv)
+  if (dtype == TL_DTYPE_F32) {
+    if (width <= 1024) TL_STORE(float, 256);
+    else if (width <= 4096) TL_STORE(float, 512);
+    else TL_STORE(float, 1024);
+  } else {
+    if (width <= 1024) TL_STORE(__nv_bfloat16, 256);
+    else if (width <= 4096) TL_STORE(__nv_bfloat16, 512);
+    else TL_STORE(__nv_bfloat16, 1024);
+  }
+#undef TL_STORE
   return TL_LAUNCH_CHECK();
 }

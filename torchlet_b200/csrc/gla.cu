@@ -49,6 +49,7 @@ gla_decay_kernel(const float* __restrict__ proj, int proj_stride, int low_offset
   float z[DECAY_TOKENS];
 #pragma unroll
   for (int tt = 0; tt < DECAY_TOKENS; ++tt) z[tt] = 0.f;
+#pragma unroll 8
   for (int j = 0; j < rank; ++j) {  // ascending j: the order depends on the rank alone
     const float w = w2t[(size_t)j * channels + c];
 #pragma unroll

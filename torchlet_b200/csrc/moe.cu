@@ -29,20 +29,20 @@ using namespace tl;
 constexpr int ROUTE_WARPS = 8;
 constexpr int MAX_EXPERTS = 256;
 
-// One router logit by one warp: each lane sums its 32nd of the row in four independent chains (k = lane,
-// lane + 32, ... in turn), so a logit's order of additions depends on the width alone, whichever kernel asks.
+// One router logit by one warp: each lane sums its 32nd of the row in eight independent chains (k = lane,
+// lane + 32, ... in turn; eight loads in flight), so a logit's order of additions depends on the width alone.
 template <typename Row>
 __device__ __forceinline__ float router_logit(const Row* __restrict__ row, const float* __restrict__ w, int hidden, int lane) {
-  float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
+  float p[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) p[i] = 0.f;
   int k = lane;
-  for (; k + 96 < hidden; k += 128) {
-    p0 = fmaf(to_float(row[k]), w[k], p0);
-    p1 = fmaf(to_float(row[k + 32]), w[k + 32], p1);
-    p2 = fmaf(to_float(row[k + 64]), w[k + 64], p2);
-    p3 = fmaf(to_float(row[k + 96]), w[k + 96], p3);
+  for (; k + 224 < hidden; k += 256) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) p[i] = fmaf(to_float(row[k + 32 * i]), w[k + 32 * i], p[i]);
   }
-  for (; k < hidden; k += 32) p0 = fmaf(to_float(row[k]), w[k], p0);
-  return warp_sum((p0 + p1) + (p2 + p3));
+  for (; k < hidden; k += 32) p[0] = fmaf(to_float(row[k]), w[k], p[0]);
+  return warp_sum(((p[0] + p[1]) + (p[2] + p[3])) + ((p[4] + p[5]) + (p[6] + p[7])));
 }
 
 // One warp: from a token's router logits (``score``, shared memory, overwritten) to its ``top`` experts and
@@ -244,19 +244,42 @@ moe_gemm_simt_kernel(const T* __restrict__ x, const T* __restrict__ w, OutT* __r
   }
 }
 
+// Four columns a thread (a block of 512 columns of one token): a thread's loads are the choices' positions and
+// one 16-byte value each, so nothing waits in a chain, and a long step still moves whole sectors.  VEC: the width
+// is a multiple of 4 (else one column a thread).
+template <bool VEC>
 __global__ void __launch_bounds__(128)
 moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ position, const float* __restrict__ weight,
                    float* __restrict__ side, int hidden, int top, int weighted) {
   tl::pdl_launch_dependents();
   tl::pdl_wait();
   const int t = blockIdx.x;
-  for (int c = threadIdx.x; c < hidden; c += 128) {
-    float sum = 0.f;
-    for (int j = 0; j < top; ++j) {
-      const float v = y[(size_t)position[(size_t)t * top + j] * hidden + c];
-      sum = weighted ? fmaf(weight[(size_t)t * top + j], v, sum) : sum + v;
+  constexpr int PER = VEC ? 4 : 1;
+  const int c = (blockIdx.y * 128 + threadIdx.x) * PER;
+  if (c >= hidden) return;
+  float sum[PER];
+#pragma unroll
+  for (int i = 0; i < PER; ++i) sum[i] = 0.f;
+  for (int j = 0; j < top; ++j) {  // in the order of the choices
+    const float* row = y + (size_t)position[(size_t)t * top + j] * hidden + c;
+    const float w = weighted ? weight[(size_t)t * top + j] : 1.f;
+    if constexpr (VEC) {
+      const float4 v = *reinterpret_cast<const float4*>(row);
+      sum[0] = weighted ? fmaf(w, v.x, sum[0]) : sum[0] + v.x;
+      sum[1] = weighted ? fmaf(w, v.y, sum[1]) : sum[1] + v.y;
+      sum[2] = weighted ? fmaf(w, v.z, sum[2]) : sum[2] + v.z;
+      sum[3] = weighted ? fmaf(w, v.w, sum[3]) : sum[3] + v.w;
+    } else {
+      sum[0] = weighted ? fmaf(w, row[0], sum[0]) : sum[0] + row[0];
     }
-    side[(size_t)t * hidden + c] += sum;
+  }
+  float* out = side + (size_t)t * hidden + c;
+  if constexpr (VEC) {
+    float4 o = *reinterpret_cast<float4*>(out);
+    o.x += sum[0]; o.y += sum[1]; o.z += sum[2]; o.w += sum[3];
+    *reinterpret_cast<float4*>(out) = o;
+  } else {
+    out[0] += sum[0];
   }
 }
 
@@ -330,8 +353,16 @@ int tl_moe_gemm_simt(const void* x, const void* w, int dtype, void* out, int out
 int tl_moe_combine(const float* y, const int* position, const float* weight, float* side, int tokens, int hidden,
                    int top, int weighted, cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  tl::launch_kernel(moe_combine_kernel, (unsigned)tokens, 128, 0, stream, y, position, weight, side, hidden, top,
-                    weighted);
+  const bool vec = hidden % 4 == 0 && ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(side)) & 15) == 0;
+  const int per_block = vec ? 512 : 128;
+  const unsigned blocks_y = (unsigned)((hidden + per_block - 1) / per_block);
+  if (blocks_y > 65535) return TL_ERR_UNSUPPORTED;
+  if (vec)
+    tl::launch_kernel(moe_combine_kernel<true>, dim3((unsigned)tokens, blocks_y), 128, 0, stream, y, position, weight, side,
+                      hidden, top, weighted);
+  else
+    tl::launch_kernel(moe_combine_kernel<false>, dim3((unsigned)tokens, blocks_y), 128, 0, stream, y, position, weight, side,
+                      hidden, top, weighted);
   return TL_LAUNCH_CHECK();
 }
 

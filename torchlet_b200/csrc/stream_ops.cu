@@ -98,7 +98,7 @@ rms_scaled_add_kernel(float* __restrict__ acc, float* __restrict__ y, const floa
 // The same for a sub-layer output of which a product left ``splits`` partial sums [splits][rows][hidden]:
 // v = y + their sum in ascending order, acc[r] += m * v * rsqrt(mean(v^2) + eps) * w; ``clear``: y is left zeroed.  The sums are taken twice
 // (once for the mean square, once for the output) rather than kept: the partial sums of a step of few tokens
-// lie in the L2.
+// lie in the L2; the first eight entries a thread owns are kept in registers instead.
 template <int NT>
 __global__ void __launch_bounds__(NT)
 rms_scaled_add_partials_kernel(float* __restrict__ acc, float* __restrict__ y, const float* __restrict__ partials,
@@ -111,20 +111,40 @@ rms_scaled_add_partials_kernel(float* __restrict__ acc, float* __restrict__ y, c
   const float* row = partials + (size_t)blockIdx.x * hidden;
   float* yrow = y + (size_t)blockIdx.x * hidden;
   float* out = acc + (size_t)blockIdx.x * hidden;
+  constexpr int KEEP = 8;
+  float kept[KEEP];
   float ss = 0.f;
-  for (int j = threadIdx.x; j < hidden; j += NT) {
+#pragma unroll
+  for (int i = 0; i < KEEP; ++i) {
+    const int j = threadIdx.x + i * NT;
+    float v = 0.f;
+    if (j < hidden) {
+      v = yrow[j];
+      for (int s = 0; s < splits; ++s) v += row[(size_t)s * plane + j];
+    }
+    kept[i] = v;
+    ss = fmaf(v, v, ss);
+  }
+  for (int j = threadIdx.x + KEEP * NT; j < hidden; j += NT) {
     float v = yrow[j];
     for (int s = 0; s < splits; ++s) v += row[(size_t)s * plane + j];
     ss = fmaf(v, v, ss);
   }
   ss = block_sum<NT>(ss, scratch);
   const float inv = rsqrtf(ss / (float)hidden + eps);
-  for (int j = threadIdx.x; j < hidden; j += NT) {
+#pragma unroll
+  for (int i = 0; i < KEEP; ++i) {
+    const int j = threadIdx.x + i * NT;
+    if (j < hidden) {
+      out[j] = fmaf(m, kept[i] * inv * w[j], out[j]);
+      yrow[j] = clear ? 0.f : kept[i];  // else y holds the finished sum, as after a finishing pass of its own
+    }
+  }
+  for (int j = threadIdx.x + KEEP * NT; j < hidden; j += NT) {
     float v = yrow[j];
     for (int s = 0; s < splits; ++s) v += row[(size_t)s * plane + j];
     out[j] = fmaf(m, v * inv * w[j], out[j]);
-    if (clear) yrow[j] = 0.f;
-    else yrow[j] = v;  // y holds the finished sum, as after a finishing pass of its own
+    yrow[j] = clear ? 0.f : v;
   }
 }
 

@@ -70,9 +70,9 @@ class SandwichBlock(Block):
     def forward(self, ctx, acc, cache) -> None:
         side = ctx.buffer("sandwich.side", tuple(acc.shape), acc.dtype)
         x = self.norms["mixer_norm"].apply(ctx, acc)
-        if ctx.plans.get("sandwich.side.clean") is not side:  # the first sandwich block of the step
+        if ctx.plans.get("sandwich.side.clean") != side.data_ptr():  # the first sandwich block of the step
             ops.fill_zero(side)
-            ctx.plans["sandwich.side.clean"] = side
+            ctx.plans["sandwich.side.clean"] = side.data_ptr()
         self.mixer.forward(ctx, x, side, cache)
         self.norms["mixer_post_norm"].add_normed(ctx, side, acc, clear=True)
         if self.feed_forward is not None:
